@@ -1,0 +1,663 @@
+"""The scheduler: shortlist -> sampled probe -> guardrail -> run -> cached schedule.
+
+Public behaviour follows the reference ``autosage/_auto.py`` (spmm_csr_auto :266-441,
+calibrate_full :444-522, sddmm_csr_auto :544-741, _csr_row_softmax :744-759,
+csr_attention_forward :762-780): same signatures, same result-dict keys, same cache records, the
+0.95 guardrail against the vendor baseline, replay-only mode.  What changed is what is being
+chosen: the candidates ``[feature_tile, warps_per_block, hub_threshold]`` now parameterise the
+sm_100a kernels behind ``torch.ops.autosage`` (tile = features per pass, warps = CTA width shared
+by a hub row, threshold = degree from which a row takes the CTA-per-hub path).
+
+Two deliberate departures, both invisible in the dict layout:
+  * hub thresholds are ranked in full-graph degree units.  The reference derives them from the
+    sampled sub-graph (whose degrees are ~3 % of the real ones, ``_auto.py:356``) and then applies
+    them to the full graph (``:402``); here the shortlist comes from the full graph and each
+    threshold is translated to the sample's matching degree quantile only for the probe.
+  * ``csr_attention_forward`` accepts ``scale`` and runs the fused one-pass kernel when it wins.
+"""
+from __future__ import annotations
+
+import os
+import statistics
+import time
+import weakref
+from typing import Any, Callable, Optional
+
+import torch
+
+from . import _native
+from ._cache import ScheduleCache, device_signature, graph_signature, log_probe, rounded_quantiles
+from .config import SchedulerConfig
+from .ops import DEFAULT_HUB_THRESHOLD, DEFAULT_WARPS, _base_flags, _normalize_csr, load_native, native_op, spmm_csr
+
+AUTOTUNE_SCHEMA_VERSION = 3
+_INF = float("inf")
+
+
+# ------------------------------------------------------------------------------------------------
+# timing
+# ------------------------------------------------------------------------------------------------
+def _time_cuda(function: Callable[[], torch.Tensor], *, warmup: int, iterations: int,
+               cap_ms: Optional[float] = None) -> dict[str, Any]:
+    """CUDA-event timing of ``function``: ``warmup`` untimed calls, then up to ``iterations`` timed
+    ones, stopping early once their sum reaches ``cap_ms``."""
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(max(warmup, 0)):
+        function()
+    torch.cuda.synchronize()
+    laps: list[float] = []
+    spent = 0.0
+    result = None
+    budget = None if cap_ms is None else max(cap_ms, 0.0)
+    for _ in range(max(iterations, 1)):
+        begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        result = function()
+        finish.record()
+        finish.synchronize()
+        lap = float(begin.elapsed_time(finish))
+        laps.append(lap)
+        spent += lap
+        if budget is not None and spent >= budget:
+            break
+    torch.cuda.synchronize()
+    return {
+        "best_ms": min(laps),
+        "mean_ms": statistics.fmean(laps),
+        "std_ms": statistics.pstdev(laps) if len(laps) > 1 else 0.0,
+        "iterations": len(laps),
+        "total_ms": spent,
+        "wall_ms": (time.perf_counter() - t0) * 1000.0,
+        "output": result,
+    }
+
+
+def _without_output(timing: dict[str, Any]) -> dict[str, Any]:
+    return {k: v for k, v in timing.items() if k != "output"}
+
+
+# ------------------------------------------------------------------------------------------------
+# baselines (the guardrail's comparators; also what "baseline" schedules run)
+# ------------------------------------------------------------------------------------------------
+def _prepare_spmm_baseline(crow, col, val, x) -> tuple[Callable[[], torch.Tensor], str]:
+    weights = torch.ones(col.numel(), device=x.device, dtype=x.dtype) if val is None else val.to(x.dtype)
+    matrix = torch.sparse_csr_tensor(crow, col, weights, size=(crow.numel() - 1, x.size(0)),
+                                     device=x.device, dtype=x.dtype)
+    return (lambda: torch.sparse.mm(matrix, x)), "torch.sparse.mm(csr)"
+
+
+def _row_ids(crow: torch.Tensor) -> torch.Tensor:
+    degrees = (crow[1:] - crow[:-1]).to(torch.long)
+    return torch.repeat_interleave(torch.arange(crow.numel() - 1, device=crow.device, dtype=torch.long), degrees)
+
+
+def _prepare_sddmm_baseline(crow, col, query, key) -> tuple[Callable[[], torch.Tensor], str]:
+    rows = _row_ids(crow)
+    return (lambda: (query.index_select(0, rows) * key.index_select(0, col)).sum(dim=1)), "gather-dot"
+
+
+# ------------------------------------------------------------------------------------------------
+# induced sample (integer outputs are bit-exact with the reference, _auto.py:95-154)
+# ------------------------------------------------------------------------------------------------
+def _induced_sample_csr(crow, col, val, *, fraction: float, minimum_rows: int, seed: int):
+    """Sub-graph induced by a seeded random row sample: keeps the edges whose row AND column are
+    sampled and relabels both to sample positions.  Returns (crow, col, val, selected_rows)."""
+    n = crow.numel() - 1
+    k = min(max(int(n * fraction), minimum_rows, 1), n)
+    device = crow.device
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    selected = torch.randperm(n, generator=gen, device=device)[:k].sort().values
+
+    new_id = torch.full((n,), -1, dtype=torch.long, device=device)
+    new_id[selected] = torch.arange(k, device=device)
+    begin = crow.index_select(0, selected)
+    degree = crow.index_select(0, selected + 1) - begin
+    total = int(degree.sum().item())
+    if total == 0:
+        empty_val = None if val is None else torch.empty(0, dtype=val.dtype, device=val.device)
+        return (torch.zeros(k + 1, dtype=torch.long, device=device),
+                torch.empty(0, dtype=torch.long, device=col.device), empty_val, selected)
+
+    owner = torch.repeat_interleave(torch.arange(k, device=device, dtype=torch.long), degree)
+    first_slot = torch.cumsum(degree, 0) - degree  # position of each sampled row's first edge
+    edge_pos = begin.index_select(0, owner) + (
+        torch.arange(total, device=device, dtype=torch.long) - first_slot.index_select(0, owner))
+    relabelled = new_id.index_select(0, col.index_select(0, edge_pos))
+    keep = relabelled >= 0
+    kept_per_row = torch.bincount(owner[keep], minlength=k)
+    sampled_crow = torch.cat((torch.zeros(1, dtype=torch.long, device=device), kept_per_row.cumsum(0)))
+    sampled_col = relabelled[keep].contiguous()
+    sampled_val = None if val is None else val.index_select(0, edge_pos)[keep].contiguous()
+    return sampled_crow, sampled_col, sampled_val, selected
+
+
+# ------------------------------------------------------------------------------------------------
+# shortlist
+# ------------------------------------------------------------------------------------------------
+def _degree_quantiles(crow: torch.Tensor) -> tuple[int, int, int]:
+    degrees = crow[1:] - crow[:-1]
+    if degrees.numel() == 0:
+        return 1, 1, 1
+    q90, q95, q99 = (max(1, q) for q in rounded_quantiles(degrees, [0.9, 0.95, 0.99]))
+    return q90, q95, q99
+
+
+def _spmm_candidates(crow: torch.Tensor, feature_width: int, config: SchedulerConfig) -> list[tuple[int, int, int]]:
+    """Up to ``candidate_count`` distinct (feature_tile, warps_per_block, hub_threshold) triples,
+    nearest first to the analytical preference: tile 64 for F <= 64 else 128; 8/4/2 warps for a
+    degree skew q99/q50 of >=4 / >=2 / less; threshold at the 95th degree percentile."""
+    q90, q95, q99 = _degree_quantiles(crow)
+    degrees = crow[1:] - crow[:-1]
+    q50 = rounded_quantiles(degrees, [0.5])[0] if degrees.numel() else 1
+    skew = q99 / max(q50, 1)
+    want_warps = 8 if skew >= 4 else (4 if skew >= 2 else 2)
+    want_tile = 64 if feature_width <= 64 else 128
+    want_threshold = q95
+
+    tile_options = [64, 128] if config.feature_tile is None else [config.feature_tile]
+    warp_options = [2, 4, 8] if config.warps_per_block is None else [config.warps_per_block]
+    if config.hub_threshold is None:
+        threshold_options = list(dict.fromkeys((q95, q90, q99)))
+    else:
+        threshold_options = [config.hub_threshold]
+
+    def distance(c: tuple[int, int, int]) -> tuple[float, tuple[int, int, int]]:
+        tile, warps, threshold = c
+        d = abs(tile - want_tile) / 64
+        d += abs(warps - want_warps) / 6
+        d += abs(threshold - want_threshold) / max(want_threshold, 1)
+        return d, c
+
+    pool = {(int(t), int(w), max(1, int(h))) for t in tile_options for w in warp_options for h in threshold_options}
+    return sorted(pool, key=distance)[: max(1, config.candidate_count)]
+
+
+def _threshold_translation(full_crow: torch.Tensor, sample_crow: torch.Tensor, config: SchedulerConfig) -> dict[int, int]:
+    """Full-graph hub threshold -> the sample's threshold at the same degree quantile."""
+    if config.hub_threshold is not None:
+        return {int(config.hub_threshold): int(config.hub_threshold)}
+    return {full: sample for full, sample in zip(_degree_quantiles(full_crow), _degree_quantiles(sample_crow))}
+
+
+# ------------------------------------------------------------------------------------------------
+# result helpers
+# ------------------------------------------------------------------------------------------------
+def _cache_hit_allowed(result: dict[str, Any], config: SchedulerConfig) -> bool:
+    if result.get("schema_version") != AUTOTUNE_SCHEMA_VERSION:
+        return False
+    return True if config.replay_only else result.get("configuration") == config.tuning_signature()
+
+
+def _cached_native_available(operation: str, choice: str, candidate: Optional[list[int]]) -> bool:
+    if choice != "autosage":
+        return True
+    return native_op(operation + ("_split" if candidate is not None else "")) is not None
+
+
+def _cpu_info(operation: str) -> dict[str, Any]:
+    return {
+        "operation": operation,
+        "schema_version": AUTOTUNE_SCHEMA_VERSION,
+        "choice": "baseline",
+        "baseline": "torch CPU",
+        "from_cache": False,
+        "reason": "AutoSAGE scheduling is CUDA-only",
+    }
+
+
+def _replay_miss(operation: str, baseline_name: str) -> dict[str, Any]:
+    return {
+        "operation": operation,
+        "schema_version": AUTOTUNE_SCHEMA_VERSION,
+        "choice": "baseline",
+        "baseline": baseline_name,
+        "from_cache": False,
+        "replay_only": True,
+        "reason": "cache miss",
+    }
+
+
+def _run_spmm_choice(choice, candidate, crow, col, val, x) -> torch.Tensor:
+    if choice == "autosage":
+        split, core = native_op("spmm_csr_split"), native_op("spmm_csr")
+        if split is not None and candidate is not None:
+            return split(crow, col, val, x, *(int(c) for c in candidate))
+        if core is not None:
+            return core(crow, col, val, x)
+    return _prepare_spmm_baseline(crow, col, val, x)[0]()
+
+
+def _run_sddmm_choice(choice, candidate, crow, col, query, key) -> torch.Tensor:
+    if choice == "autosage":
+        split, core = native_op("sddmm_csr_split"), native_op("sddmm_csr")
+        if split is not None and candidate is not None:
+            return split(crow, col, query, key, *(int(c) for c in candidate))
+        if core is not None:
+            return core(crow, col, query, key)
+    return _prepare_sddmm_baseline(crow, col, query, key)[0]()
+
+
+# ------------------------------------------------------------------------------------------------
+# the probe engine shared by SpMM, SDDMM and fused attention
+# ------------------------------------------------------------------------------------------------
+class _Memo:
+    """graph_signature memo: the signature sorts all degrees and copies 4096 indices to the host,
+    which would otherwise happen on every replayed call.  Entries die with their tensors."""
+
+    def __init__(self) -> None:
+        self._entries: dict[tuple, tuple] = {}
+
+    def signature(self, crow, col, width, operation, weighted, dtype) -> dict[str, Any]:
+        key = (crow.data_ptr(), col.data_ptr(), crow.numel(), col.numel(), int(width), operation, bool(weighted), str(dtype))
+        hit = self._entries.get(key)
+        if hit is not None:
+            crow_ref, col_ref, versions, value = hit
+            if crow_ref() is crow and col_ref() is col and versions == (crow._version, col._version):
+                return dict(value)
+        value = graph_signature(crow, col, width, operation, weighted=weighted, dtype=dtype)
+        if len(self._entries) > 64:
+            self._entries.clear()
+        self._entries[key] = (weakref.ref(crow), weakref.ref(col), (crow._version, col._version), dict(value))
+        return value
+
+
+_SIGNATURES = _Memo()
+
+
+def _probe_and_choose(
+    *,
+    operation: str,
+    label: str,
+    config: SchedulerConfig,
+    device: dict[str, Any],
+    graph: dict[str, Any],
+    cache: ScheduleCache,
+    sample_ms: float,
+    probe_rows: int,
+    probe_nonzeros: int,
+    baseline: Callable[[], torch.Tensor],
+    baseline_name: str,
+    candidates: list[tuple[list[int], Callable[[], torch.Tensor]]],
+    fallback: Optional[Callable[[], torch.Tensor]],
+    verbose: bool,
+) -> dict[str, Any]:
+    """Times the baseline and the shortlisted candidates on the sample under the probe budget and
+    applies the guardrail.  ``candidates`` pairs the full-graph parameter list stored in the
+    schedule with a closure running it on the sample; ``fallback`` is the parameter-free native
+    kernel used when hub splitting is disabled."""
+    base = _time_cuda(baseline, warmup=1, iterations=config.probe_iterations)
+    timings: list[dict[str, Any]] = []
+    best, best_params = _INF, None
+    remaining = config.probe_cap_ms
+    if candidates:
+        for index, (params, run) in enumerate(candidates):
+            if index > 0 and remaining <= 0.0:
+                break
+            lap = _time_cuda(run, warmup=1, iterations=config.probe_iterations, cap_ms=max(0.0, remaining))
+            remaining = max(0.0, remaining - lap["total_ms"])
+            timings.append({"candidate": list(params), **_without_output(lap)})
+            if lap["best_ms"] < best:
+                best, best_params = lap["best_ms"], list(params)
+    elif fallback is not None:
+        lap = _time_cuda(fallback, warmup=1, iterations=config.probe_iterations, cap_ms=config.probe_cap_ms)
+        best = lap["best_ms"]
+        timings.append({"candidate": None, **_without_output(lap)})
+
+    enough = probe_rows >= config.minimum_probe_rows and probe_nonzeros >= config.minimum_probe_nonzeros
+    wins = enough and best <= config.guardrail * base["best_ms"]
+    result = {
+        "operation": operation,
+        "schema_version": AUTOTUNE_SCHEMA_VERSION,
+        "choice": "autosage" if wins else "baseline",
+        "candidate": best_params if wins else None,
+        "baseline": baseline_name,
+        "guardrail": config.guardrail,
+        "configuration": config.tuning_signature(),
+        "probe_rows": int(probe_rows),
+        "probe_nonzeros": int(probe_nonzeros),
+        "sampling_ms": sample_ms,
+        "probe_ms": sample_ms + base["wall_ms"] + sum(t["wall_ms"] for t in timings),
+        "baseline_probe_ms": base["best_ms"],
+        "autosage_probe_ms": None if best == _INF else best,
+        "sampled_speedup": (base["best_ms"] / best) if best not in (0.0, _INF) else None,
+        "candidates": timings,
+        "from_cache": False,
+    }
+    if config.cache:
+        cache.store(device, graph, result)
+    log_probe({"timestamp": time.time(), "device": device, "graph": graph, "result": result})
+    if verbose or os.getenv("AUTOSAGE_VERBOSE") == "1":
+        print(f"[autosage:{label}] rows={result['probe_rows']} nnz={result['probe_nonzeros']} "
+              f"baseline={result['baseline_probe_ms']:.4f} ms auto={result['autosage_probe_ms']} "
+              f"choice={result['choice']}")
+    return result
+
+
+def _lookup(cache: ScheduleCache, config: SchedulerConfig, device, graph, op_name: str) -> Optional[dict[str, Any]]:
+    if not config.cache:
+        return None
+    record = cache.lookup(device, graph)
+    if record is None:
+        return None
+    result = record.get("result", {})
+    if not _cache_hit_allowed(result, config):
+        return None
+    if not _cached_native_available(op_name, result.get("choice", "baseline"), result.get("candidate")):
+        return None
+    return result
+
+
+def _timed_sample(crow, col, val, config: SchedulerConfig, seed: int):
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    sample = _induced_sample_csr(crow, col, val, fraction=config.probe_fraction,
+                                 minimum_rows=config.probe_min_rows, seed=seed)
+    return sample, t0
+
+
+# ------------------------------------------------------------------------------------------------
+# SpMM
+# ------------------------------------------------------------------------------------------------
+def spmm_csr_auto(crow, col, val, x, *, guardrail: float = 0.95, k: int = 6, seed: int = 0,
+                  verbose: bool = False) -> tuple[torch.Tensor, dict[str, Any]]:
+    crow, col, val, x = _normalize_csr(crow, col, val, x)
+    if not x.is_cuda:
+        return spmm_csr(crow, col, val, x), _cpu_info("spmm")
+    if x.dtype != torch.float32:
+        run, name = _prepare_spmm_baseline(crow, col, val, x)
+        return run(), {**_cpu_info("spmm"), "baseline": name,
+                       "reason": "AutoSAGE CUDA kernels require float32 features"}
+
+    load_native()
+    config = SchedulerConfig.from_env(guardrail=guardrail, candidate_count=k)
+    device = device_signature()
+    graph = _SIGNATURES.signature(crow, col, x.size(1), "spmm", val is not None, x.dtype)
+    cache = ScheduleCache()
+
+    hit = _lookup(cache, config, device, graph, "spmm_csr")
+    if hit is not None:
+        output = _run_spmm_choice(hit.get("choice", "baseline"), hit.get("candidate"), crow, col, val, x)
+        return output, {**hit, "from_cache": True}
+    if config.replay_only:
+        return _run_spmm_choice("baseline", None, crow, col, val, x), _replay_miss("spmm", "torch.sparse.mm(csr)")
+
+    (s_crow, s_col, s_val, selected), t0 = _timed_sample(crow, col, val, config, seed)
+    s_x = x.index_select(0, selected).contiguous()
+    torch.cuda.synchronize()
+    sample_ms = (time.perf_counter() - t0) * 1000.0
+
+    baseline, baseline_name = _prepare_spmm_baseline(s_crow, s_col, s_val, s_x)
+    split = native_op("spmm_csr_split") if config.hub_split else None
+    core = native_op("spmm_csr")
+    runs: list[tuple[list[int], Callable[[], torch.Tensor]]] = []
+    if split is not None:
+        to_sample = _threshold_translation(crow, s_crow, config)
+        for tile, warps, threshold in _spmm_candidates(crow, x.size(1), config):
+            probe_threshold = max(1, to_sample.get(threshold, threshold))
+            runs.append(([tile, warps, threshold],
+                         lambda t=tile, w=warps, h=probe_threshold: split(s_crow, s_col, s_val, s_x, t, w, h)))
+    result = _probe_and_choose(
+        operation="spmm", label="spmm", config=config, device=device, graph=graph, cache=cache,
+        sample_ms=sample_ms, probe_rows=s_crow.numel() - 1, probe_nonzeros=s_col.numel(),
+        baseline=baseline, baseline_name=baseline_name, candidates=runs,
+        fallback=(lambda: core(s_crow, s_col, s_val, s_x)) if core is not None else None, verbose=verbose)
+    output = _run_spmm_choice(result["choice"], result["candidate"] if result["choice"] == "autosage" else None,
+                              crow, col, val, x)
+    return output, result
+
+
+def calibrate_full(crow, col, val, x, guardrail: float = 0.95) -> tuple[str, dict[str, Any]]:
+    """Times the baseline and every shortlisted candidate on the FULL graph and stores the winner."""
+    crow, col, val, x = _normalize_csr(crow, col, val, x)
+    if not x.is_cuda:
+        return "baseline", _cpu_info("spmm")
+    if x.dtype != torch.float32:
+        return "baseline", {**_cpu_info("spmm"), "baseline": "torch.sparse.mm(csr)",
+                            "reason": "AutoSAGE CUDA kernels require float32 features"}
+    load_native()
+    config = SchedulerConfig.from_env(guardrail=guardrail, candidate_count=6)
+    baseline, baseline_name = _prepare_spmm_baseline(crow, col, val, x)
+    base = _time_cuda(baseline, warmup=2, iterations=5)
+    split = native_op("spmm_csr_split") if config.hub_split else None
+    core = native_op("spmm_csr")
+    best, winner = _INF, None
+    laps: list[dict[str, Any]] = []
+    if split is not None:
+        for tile, warps, threshold in _spmm_candidates(crow, x.size(1), config):
+            lap = _time_cuda(lambda t=tile, w=warps, h=threshold: split(crow, col, val, x, t, w, h),
+                             warmup=2, iterations=5)
+            laps.append({"candidate": [tile, warps, threshold], "best_ms": lap["best_ms"]})
+            if lap["best_ms"] < best:
+                best, winner = lap["best_ms"], [tile, warps, threshold]
+    elif core is not None:
+        best = _time_cuda(lambda: core(crow, col, val, x), warmup=2, iterations=5)["best_ms"]
+        laps.append({"candidate": None, "best_ms": best})
+    choice = "autosage" if best <= guardrail * base["best_ms"] else "baseline"
+    result = {
+        "operation": "spmm",
+        "schema_version": AUTOTUNE_SCHEMA_VERSION,
+        "choice": choice,
+        "candidate": winner if choice == "autosage" else None,
+        "baseline": baseline_name,
+        "guardrail": guardrail,
+        "configuration": config.tuning_signature(),
+        "calibration": "full_graph",
+        "baseline_ms": base["best_ms"],
+        "autosage_ms": None if best == _INF else best,
+        "speedup": (base["best_ms"] / best) if best not in (0.0, _INF) else None,
+        "candidates": laps,
+        "from_cache": False,
+    }
+    device = device_signature()
+    graph = graph_signature(crow, col, x.size(1), "spmm", weighted=val is not None, dtype=x.dtype)
+    if config.cache:
+        ScheduleCache().store(device, graph, result)
+    log_probe({"timestamp": time.time(), "device": device, "graph": graph, "result": result})
+    return choice, result
+
+
+# ------------------------------------------------------------------------------------------------
+# SDDMM
+# ------------------------------------------------------------------------------------------------
+def _normalize_sddmm(crow, col, query, key):
+    if crow.dtype not in (torch.int32, torch.int64) or col.dtype not in (torch.int32, torch.int64):
+        raise TypeError("crow and col must use integer indices")
+    crow, col = crow.to(torch.long).contiguous(), col.to(torch.long).contiguous()
+    query, key = query.contiguous(), key.contiguous()
+    if query.ndim != 2 or query.shape != key.shape:
+        raise ValueError("query and key must have the same [N, F] shape")
+    if not query.is_floating_point() or query.dtype != key.dtype:
+        raise TypeError("query and key must use the same floating-point dtype")
+    if crow.ndim != 1 or col.ndim != 1:
+        raise ValueError("crow and col must be one-dimensional")
+    if crow.numel() != query.size(0) + 1:
+        raise ValueError("crow must contain N + 1 entries")
+    if not (crow.device == col.device == query.device == key.device):
+        raise ValueError("all SDDMM inputs must be on the same device")
+    return crow, col, query, key
+
+
+def _warp_threshold_pairs(crow, width, config) -> list[tuple[int, int]]:
+    return list(dict.fromkeys((w, h) for _, w, h in _spmm_candidates(crow, width, config)))
+
+
+def sddmm_csr_auto(crow, col, query, key, *, guardrail: float = 0.95, seed: int = 0,
+                   verbose: bool = False) -> tuple[torch.Tensor, dict[str, Any]]:
+    crow, col, query, key = _normalize_sddmm(crow, col, query, key)
+    if not query.is_cuda:
+        run, name = _prepare_sddmm_baseline(crow, col, query, key)
+        return run(), {**_cpu_info("sddmm"), "baseline": name}
+    if query.dtype != torch.float32:
+        run, name = _prepare_sddmm_baseline(crow, col, query, key)
+        return run(), {**_cpu_info("sddmm"), "baseline": name,
+                       "reason": "AutoSAGE CUDA kernels require float32 features"}
+
+    load_native()
+    config = SchedulerConfig.from_env(guardrail=guardrail, candidate_count=6)
+    device = device_signature()
+    graph = _SIGNATURES.signature(crow, col, query.size(1), "sddmm", False, query.dtype)
+    cache = ScheduleCache()
+
+    hit = _lookup(cache, config, device, graph, "sddmm_csr")
+    if hit is not None:
+        output = _run_sddmm_choice(hit.get("choice", "baseline"), hit.get("candidate"), crow, col, query, key)
+        return output, {**hit, "from_cache": True}
+    if config.replay_only:
+        return _run_sddmm_choice("baseline", None, crow, col, query, key), _replay_miss("sddmm", "gather-dot")
+
+    (s_crow, s_col, _, selected), t0 = _timed_sample(crow, col, None, config, seed)
+    s_query = query.index_select(0, selected).contiguous()
+    s_key = key.index_select(0, selected).contiguous()
+    torch.cuda.synchronize()
+    sample_ms = (time.perf_counter() - t0) * 1000.0
+
+    baseline, baseline_name = _prepare_sddmm_baseline(s_crow, s_col, s_query, s_key)
+    split = native_op("sddmm_csr_split") if config.hub_split else None
+    core = native_op("sddmm_csr")
+    runs: list[tuple[list[int], Callable[[], torch.Tensor]]] = []
+    if split is not None:
+        to_sample = _threshold_translation(crow, s_crow, config)
+        for warps, threshold in _warp_threshold_pairs(crow, query.size(1), config):
+            probe_threshold = max(1, to_sample.get(threshold, threshold))
+            runs.append(([warps, threshold],
+                         lambda w=warps, h=probe_threshold: split(s_crow, s_col, s_query, s_key, w, h)))
+    result = _probe_and_choose(
+        operation="sddmm", label="sddmm", config=config, device=device, graph=graph, cache=cache,
+        sample_ms=sample_ms, probe_rows=s_crow.numel() - 1, probe_nonzeros=s_col.numel(),
+        baseline=baseline, baseline_name=baseline_name, candidates=runs,
+        fallback=(lambda: core(s_crow, s_col, s_query, s_key)) if core is not None else None, verbose=verbose)
+    output = _run_sddmm_choice(result["choice"], result["candidate"] if result["choice"] == "autosage" else None,
+                               crow, col, query, key)
+    return output, result
+
+
+# ------------------------------------------------------------------------------------------------
+# softmax and attention
+# ------------------------------------------------------------------------------------------------
+def _csr_row_softmax(crow: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
+    """Softmax over each CSR row segment of ``scores``.  float32 CUDA inputs run the segmented
+    kernel; everything else runs the reference's scatter formulation (``_auto.py:744-759``)."""
+    if scores.numel() == 0:
+        return scores.clone()
+    if scores.is_cuda and scores.dtype == torch.float32 and crow.dtype == torch.long and load_native():
+        crow = crow.contiguous()
+        scores = scores.contiguous()
+        probs = torch.empty_like(scores)
+        workspace, ready = _native.planned_workspace(crow, DEFAULT_HUB_THRESHOLD)
+        _native.row_softmax(crow, scores, probs, warps=DEFAULT_WARPS, threshold=DEFAULT_HUB_THRESHOLD,
+                            flags=ready, workspace=workspace)
+        return probs
+    rows = _row_ids(crow)
+    peak = torch.full((crow.numel() - 1,), -torch.inf, dtype=scores.dtype, device=scores.device)
+    peak.scatter_reduce_(0, rows, scores, reduce="amax", include_self=True)
+    shifted = (scores - peak.index_select(0, rows)).exp()
+    total = torch.zeros_like(peak).scatter_add_(0, rows, shifted)
+    return shifted / total.index_select(0, rows)
+
+
+def _fused_attention_enabled() -> bool:
+    return os.getenv("AUTOSAGE_FUSED_ATTENTION", "1").strip().lower() not in {"0", "false", "no", "off"}
+
+
+def _attention_unfused(crow, col, query, key, value, scale, guardrail, seed, verbose):
+    scaled_query = query if scale is None else query * scale
+    scores, sddmm_info = sddmm_csr_auto(crow, col, scaled_query, key, guardrail=guardrail, seed=seed, verbose=verbose)
+    probabilities = _csr_row_softmax(crow.to(torch.long), scores.to(query.dtype))
+    output, spmm_info = spmm_csr_auto(crow, col, probabilities, value, guardrail=guardrail, seed=seed, verbose=verbose)
+    return output, {"sddmm": sddmm_info, "spmm": spmm_info}
+
+
+def _run_fused_attention(crow, col, query, key, value, scale, warps, threshold) -> torch.Tensor:
+    out = torch.empty_like(value)
+    if out.numel() == 0:
+        return out
+    workspace, ready = _native.planned_workspace(crow, threshold)
+    _native.attention(crow, col, query, key, value, out, scale=1.0 if scale is None else float(scale),
+                      warps=warps, threshold=threshold, flags=_base_flags() | ready, workspace=workspace)
+    return out
+
+
+def csr_attention_forward(crow, col, query, key, value, *, guardrail: float = 0.95, seed: int = 0,
+                          verbose: bool = False, scale: Optional[float] = None,
+                          fused: Optional[bool] = None) -> tuple[torch.Tensor, dict[str, Any]]:
+    """softmax_row(scale * Q K^T on the CSR pattern) V.
+
+    ``scale=None`` is the reference behaviour (no scaling, ``_auto.py:762-780``).  On float32 CUDA
+    inputs with at most 512 features the one-pass fused kernel is scheduled like the other
+    operators (probe on the induced sample against the three-pass pipeline, guardrail, cache under
+    operation "attention"); ``fused=False`` or AUTOSAGE_FUSED_ATTENTION=0 forces the reference's
+    three-pass composition.  The info dict keeps the reference's two keys and adds "attention".
+    """
+    use_fused = _fused_attention_enabled() if fused is None else bool(fused)
+    eligible = (query.is_cuda and query.dtype == torch.float32 and key.dtype == torch.float32
+                and value.dtype == torch.float32 and query.ndim == 2 and query.shape == key.shape == value.shape
+                and query.size(1) <= 512)
+    if not (use_fused and eligible):
+        return _attention_unfused(crow, col, query, key, value, scale, guardrail, seed, verbose)
+
+    crow, col, query, key = _normalize_sddmm(crow, col, query, key)
+    value = value.contiguous()
+    load_native()
+    config = SchedulerConfig.from_env(guardrail=guardrail, candidate_count=6)
+    device = device_signature()
+    graph = _SIGNATURES.signature(crow, col, query.size(1), "attention", False, query.dtype)
+    cache = ScheduleCache()
+
+    def finish(result: dict[str, Any], from_cache: bool):
+        if result.get("choice") == "autosage" and result.get("candidate") is not None:
+            warps, threshold = (int(c) for c in result["candidate"])
+            output = _run_fused_attention(crow, col, query, key, value, scale, warps, threshold)
+            info = {**result, "from_cache": from_cache}
+            stage = {"operation": None, "schema_version": AUTOTUNE_SCHEMA_VERSION, "choice": "autosage",
+                     "candidate": result["candidate"], "fused": True, "from_cache": from_cache}
+            return output, {"sddmm": {**stage, "operation": "sddmm"}, "spmm": {**stage, "operation": "spmm"},
+                            "attention": info}
+        output, infos = _attention_unfused(crow, col, query, key, value, scale, guardrail, seed, verbose)
+        return output, {**infos, "attention": {**result, "from_cache": from_cache}}
+
+    hit = None
+    if config.cache:
+        record = cache.lookup(device, graph)
+        if record is not None and _cache_hit_allowed(record.get("result", {}), config):
+            hit = record["result"]
+    if hit is not None:
+        return finish(hit, True)
+    if config.replay_only:
+        return finish(_replay_miss("attention", "sddmm+softmax+spmm"), False)
+
+    (s_crow, s_col, _, selected), t0 = _timed_sample(crow, col, None, config, seed)
+    s_q = query.index_select(0, selected).contiguous()
+    s_k = key.index_select(0, selected).contiguous()
+    s_v = value.index_select(0, selected).contiguous()
+    torch.cuda.synchronize()
+    sample_ms = (time.perf_counter() - t0) * 1000.0
+
+    sddmm_core, spmm_core = native_op("sddmm_csr"), native_op("spmm_csr")
+
+    def three_pass() -> torch.Tensor:
+        q = s_q if scale is None else s_q * scale
+        scores = sddmm_core(s_crow, s_col, q, s_k)
+        return spmm_core(s_crow, s_col, _csr_row_softmax(s_crow, scores), s_v)
+
+    to_sample = _threshold_translation(crow, s_crow, config)
+    runs = []
+    for warps, threshold in _warp_threshold_pairs(crow, query.size(1), config):
+        probe_threshold = max(1, to_sample.get(threshold, threshold))
+        runs.append(([warps, threshold],
+                     lambda w=warps, h=probe_threshold: _run_fused_attention(s_crow, s_col, s_q, s_k, s_v, scale, w, h)))
+    result = _probe_and_choose(
+        operation="attention", label="attention", config=config, device=device, graph=graph, cache=cache,
+        sample_ms=sample_ms, probe_rows=s_crow.numel() - 1, probe_nonzeros=s_col.numel(),
+        baseline=three_pass, baseline_name="sddmm+softmax+spmm", candidates=runs, fallback=None, verbose=verbose)
+    return finish(result, False)
+
+
+__all__ = [
+    "AUTOTUNE_SCHEMA_VERSION",
+    "calibrate_full",
+    "csr_attention_forward",
+    "sddmm_csr_auto",
+    "spmm_csr_auto",
+]

@@ -1,0 +1,241 @@
+"""ctypes binding of ``libautosage_b200.so`` (the C ABI declared in ``include/autosage_b200.h``).
+
+Nothing here computes: every function forwards device pointers and sizes to the CUDA library and
+turns a negative status code into ``RuntimeError`` (the reference's ``TORCH_CHECK`` failures surface
+as ``RuntimeError`` too).  There is deliberately no CPU or PyTorch fallback: if the library cannot
+be loaded the callers raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import weakref
+from collections import OrderedDict
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+LIB_NAMES = ("libautosage_b200.so",)
+
+FLAG_ACCUMULATE = 1
+FLAG_NO_VEC4 = 2
+FLAG_PLAN_READY = 4
+FLAG_NO_BULK_STAGE = 8
+
+_P = ctypes.c_void_p
+_I64 = ctypes.c_int64
+_INT = ctypes.c_int
+_U32 = ctypes.c_uint
+_SZ = ctypes.c_size_t
+_F32 = ctypes.c_float
+
+# name -> (restype, argtypes); kept in the order of the header
+SIGNATURES = {
+    "asg_version": (_INT, []),
+    "asg_last_error_string": (ctypes.c_char_p, []),
+    "asg_workspace_bytes": (_SZ, [_I64]),
+    "asg_plan_build": (_INT, [_P, _I64, _I64, _P, _SZ, _P]),
+    "asg_plan_export": (_INT, [_P, _I64, _P, _P, _P]),
+    "asg_spmm_csr": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
+    "asg_spmm_csr_split": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _P, _SZ, _P]),
+    "asg_spmm_csr_ex": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _U32, _P, _SZ, _P]),
+    "asg_sddmm_csr": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
+    "asg_sddmm_csr_split": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _I64, _P, _SZ, _P]),
+    "asg_sddmm_csr_ex": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
+    "asg_csr_row_softmax": (_INT, [_P, _P, _P, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
+    "asg_csr_attention": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _F32, _INT, _I64, _U32, _P, _SZ, _P]),
+    "asg_workspace_status": (_INT, [_P, _P, _P]),
+}
+
+_LIB: Optional[ctypes.CDLL] = None
+_LIB_PATH: Optional[str] = None
+
+
+def candidate_libraries() -> list[Path]:
+    """Search order, mirroring the reference loader (autosage/ops.py:14-28): the explicit
+    ``AUTOSAGE_NATIVE_PATH``, then ``<repo>/build/``, then the package's ``lib/`` directory."""
+    package = Path(__file__).resolve().parent
+    paths: list[Path] = []
+    explicit = os.getenv("AUTOSAGE_NATIVE_PATH")
+    if explicit:
+        paths.append(Path(explicit).expanduser())
+    for directory in (package.parent / "build", package / "lib"):
+        paths.extend(directory / name for name in LIB_NAMES)
+    return paths
+
+
+def bind(path: str) -> ctypes.CDLL:
+    """Load the shared library at ``path`` and attach the prototypes; raises ``OSError`` if the file
+    cannot be loaded and ``RuntimeError`` if it lacks a declared symbol."""
+    lib = ctypes.CDLL(path)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise RuntimeError(f"{path} does not export {name}") from exc
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+def set_library(lib: ctypes.CDLL, path: str) -> None:
+    global _LIB, _LIB_PATH
+    _LIB = lib
+    _LIB_PATH = path
+
+
+def library() -> ctypes.CDLL:
+    if _LIB is None:
+        raise RuntimeError("libautosage_b200.so is not loaded; call autosage_b200.load_native() first")
+    return _LIB
+
+
+def library_path() -> Optional[str]:
+    return _LIB_PATH
+
+
+def check(code: int) -> None:
+    if code != 0:
+        message = library().asg_last_error_string()
+        text = message.decode("utf-8", "replace") if message else ""
+        raise RuntimeError(f"{text} (autosage_b200 status {code})")
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+# --------------------------------------------------------------------------------------------
+# Workspaces.  The C ABI never allocates; scratch comes from torch's caching allocator so it
+# follows torch's stream semantics.  One scratch buffer per (device, stream) is kept for calls that
+# rebuild the plan, and a small LRU of buffers holding finished plans is keyed by the crow tensor.
+# --------------------------------------------------------------------------------------------
+_SCRATCH: dict[tuple[int, int], torch.Tensor] = {}
+_PLANS: "OrderedDict[tuple, tuple]" = OrderedDict()
+PLAN_CACHE_ENTRIES = 16
+
+
+def workspace_bytes(n_rows: int) -> int:
+    return int(library().asg_workspace_bytes(int(n_rows)))
+
+
+def scratch(device: torch.device, n_rows: int) -> torch.Tensor:
+    need = workspace_bytes(n_rows)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream(device))
+    buffer = _SCRATCH.get(key)
+    if buffer is None or buffer.numel() < need:
+        buffer = torch.empty(max(need, 1 << 16), dtype=torch.uint8, device=device)
+        _SCRATCH[key] = buffer
+    return buffer
+
+
+def planned_workspace(crow: torch.Tensor, threshold: int) -> tuple[torch.Tensor, int]:
+    """Workspace holding the degree-binned plan of ``crow`` for ``threshold``.
+
+    Returns ``(buffer, flags)`` where flags is ``FLAG_PLAN_READY`` when the buffer already holds
+    the plan (same tensor object, same version counter) and 0 when the callee must build it.
+    """
+    if os.getenv("AUTOSAGE_PLAN_CACHE", "1") in ("0", "false", "off", "no"):
+        return scratch(crow.device, crow.numel() - 1), 0
+    key = (crow.data_ptr(), crow.numel(), int(threshold), crow.device.index, _stream(crow.device))
+    entry = _PLANS.get(key)
+    if entry is not None:
+        ref, version, buffer = entry
+        if ref() is crow and version == crow._version:
+            _PLANS.move_to_end(key)
+            return buffer, FLAG_PLAN_READY
+        del _PLANS[key]
+    buffer = torch.empty(max(workspace_bytes(crow.numel() - 1), 256), dtype=torch.uint8, device=crow.device)
+    _PLANS[key] = (weakref.ref(crow), crow._version, buffer)
+    while len(_PLANS) > PLAN_CACHE_ENTRIES:
+        _PLANS.popitem(last=False)
+    return buffer, 0
+
+
+def clear_plan_cache() -> None:
+    _PLANS.clear()
+    _SCRATCH.clear()
+
+
+# --------------------------------------------------------------------------------------------
+# Thin wrappers (tensors in, status checked).  Inputs must already be validated and contiguous.
+# --------------------------------------------------------------------------------------------
+def plan_build(crow: torch.Tensor, threshold: int, workspace: torch.Tensor) -> None:
+    check(library().asg_plan_build(crow.data_ptr(), crow.numel() - 1, int(threshold), workspace.data_ptr(),
+                                   workspace.numel(), _stream(crow.device)))
+
+
+def plan_export(workspace: torch.Tensor, n_rows: int) -> tuple[torch.Tensor, torch.Tensor]:
+    order = torch.empty(n_rows, dtype=torch.int32, device=workspace.device)
+    counts = torch.empty(2, dtype=torch.int32, device=workspace.device)
+    check(library().asg_plan_export(workspace.data_ptr(), n_rows, order.data_ptr(), counts.data_ptr(),
+                                    _stream(workspace.device)))
+    return order, counts
+
+
+def spmm(crow, col, val, x, y, *, feature_tile: int, warps: int, threshold: int, flags: int,
+         workspace: torch.Tensor) -> None:
+    check(library().asg_spmm_csr_ex(crow.data_ptr(), col.data_ptr(), _ptr(val), x.data_ptr(), y.data_ptr(),
+                                    y.size(0), col.numel(), x.size(1), int(feature_tile), int(warps),
+                                    int(threshold), int(flags), workspace.data_ptr(), workspace.numel(),
+                                    _stream(x.device)))
+
+
+def spmm_split_strict(crow, col, val, x, y, feature_tile: int, warps: int, threshold: int,
+                      workspace: torch.Tensor) -> None:
+    check(library().asg_spmm_csr_split(crow.data_ptr(), col.data_ptr(), _ptr(val), x.data_ptr(), y.data_ptr(),
+                                       y.size(0), col.numel(), x.size(1), int(feature_tile), int(warps),
+                                       int(threshold), workspace.data_ptr(), workspace.numel(), _stream(x.device)))
+
+
+def spmm_plain(crow, col, val, x, y, workspace: torch.Tensor) -> None:
+    check(library().asg_spmm_csr(crow.data_ptr(), col.data_ptr(), _ptr(val), x.data_ptr(), y.data_ptr(),
+                                 y.size(0), col.numel(), x.size(1), workspace.data_ptr(), workspace.numel(),
+                                 _stream(x.device)))
+
+
+def sddmm(crow, col, query, key, out, *, warps: int, threshold: int, flags: int, workspace: torch.Tensor) -> None:
+    check(library().asg_sddmm_csr_ex(crow.data_ptr(), col.data_ptr(), query.data_ptr(), key.data_ptr(),
+                                     out.data_ptr(), query.size(0), col.numel(), query.size(1), int(warps),
+                                     int(threshold), int(flags), workspace.data_ptr(), workspace.numel(),
+                                     _stream(query.device)))
+
+
+def sddmm_split_strict(crow, col, query, key, out, warps: int, threshold: int, workspace: torch.Tensor) -> None:
+    check(library().asg_sddmm_csr_split(crow.data_ptr(), col.data_ptr(), query.data_ptr(), key.data_ptr(),
+                                        out.data_ptr(), query.size(0), col.numel(), query.size(1), int(warps),
+                                        int(threshold), workspace.data_ptr(), workspace.numel(),
+                                        _stream(query.device)))
+
+
+def sddmm_plain(crow, col, query, key, out, workspace: torch.Tensor) -> None:
+    check(library().asg_sddmm_csr(crow.data_ptr(), col.data_ptr(), query.data_ptr(), key.data_ptr(),
+                                  out.data_ptr(), query.size(0), col.numel(), query.size(1),
+                                  workspace.data_ptr(), workspace.numel(), _stream(query.device)))
+
+
+def row_softmax(crow, scores, probs, *, warps: int, threshold: int, flags: int, workspace: torch.Tensor) -> None:
+    check(library().asg_csr_row_softmax(crow.data_ptr(), scores.data_ptr(), probs.data_ptr(), crow.numel() - 1,
+                                        scores.numel(), int(warps), int(threshold), int(flags),
+                                        workspace.data_ptr(), workspace.numel(), _stream(scores.device)))
+
+
+def attention(crow, col, query, key, value, out, *, scale: float, warps: int, threshold: int, flags: int,
+              workspace: torch.Tensor) -> None:
+    check(library().asg_csr_attention(crow.data_ptr(), col.data_ptr(), query.data_ptr(), key.data_ptr(),
+                                      value.data_ptr(), out.data_ptr(), query.size(0), col.numel(),
+                                      query.size(1), float(scale), int(warps), int(threshold), int(flags),
+                                      workspace.data_ptr(), workspace.numel(), _stream(query.device)))
+
+
+def workspace_status(workspace: torch.Tensor) -> int:
+    """Synchronising read of the status word kernels set when a bounded wait expired."""
+    host = ctypes.c_int32(0)
+    check(library().asg_workspace_status(workspace.data_ptr(), ctypes.byref(host), _stream(workspace.device)))
+    torch.cuda.current_stream(workspace.device).synchronize()
+    return int(host.value)

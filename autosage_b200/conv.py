@@ -1,0 +1,67 @@
+"""``AutoSAGEConv``: neighbourhood aggregation (CSR SpMM over destination rows) + ``nn.Linear``.
+
+Interface of the reference layer (``autosage/conv.py:13-56``): ``AutoSAGEConv(in_channels,
+out_channels, *, mode="auto"|"native", bias=True)`` and ``forward(x, edge_index, edge_weight=None,
+*, return_info=False)``.  The CSR build is memoised per ``edge_index`` tensor, so repeated forwards
+over one graph do not re-sort the edges (the reference re-sorts on every call, ``conv.py:36,44``).
+"""
+from __future__ import annotations
+
+import weakref
+from typing import Optional
+
+import torch
+from torch import nn
+
+from ._auto import spmm_csr_auto
+from .ops import spmm_csr
+from .utils.csr import edge_index_to_csr
+
+
+class _CsrMemo:
+    """Last (edge_index -> crow, col, edge permutation) conversion, valid while the same tensor object
+    is passed again unmodified."""
+
+    def __init__(self) -> None:
+        self._ref = None
+        self._version = -1
+        self._nodes = -1
+        self._value = None
+
+    def get(self, edge_index: torch.Tensor, num_nodes: int, need_order: bool):
+        same = (self._ref is not None and self._ref() is edge_index and self._version == edge_index._version
+                and self._nodes == num_nodes)
+        if not same:
+            crow, col = edge_index_to_csr(edge_index, num_nodes, rows_by="dst")
+            self._ref, self._version, self._nodes = weakref.ref(edge_index), edge_index._version, num_nodes
+            self._value = [crow, col, None]
+        if need_order and self._value[2] is None:
+            self._value[2] = edge_index[1].to(torch.long).argsort(stable=True)
+        return self._value
+
+
+class AutoSAGEConv(nn.Module):
+    def __init__(self, in_channels: int, out_channels: int, *, mode: str = "auto", bias: bool = True) -> None:
+        super().__init__()
+        if mode not in ("auto", "native"):
+            raise ValueError("mode must be 'auto' or 'native'")
+        self.linear = nn.Linear(in_channels, out_channels, bias=bias)
+        self.mode = mode
+        self._csr = _CsrMemo()
+
+    def forward(self, x: torch.Tensor, edge_index: torch.Tensor, edge_weight: Optional[torch.Tensor] = None, *,
+                return_info: bool = False):
+        if edge_weight is not None:
+            if edge_weight.ndim != 1 or edge_weight.numel() != edge_index.size(1):
+                raise ValueError("edge_weight must contain one value per edge")
+            if edge_weight.device != edge_index.device:
+                raise ValueError("edge_weight and edge_index must be on the same device")
+        crow, col, order = self._csr.get(edge_index, x.size(0), edge_weight is not None)
+        weights = None if edge_weight is None else edge_weight.index_select(0, order)
+        if self.mode == "auto":
+            aggregated, info = spmm_csr_auto(crow, col, weights, x)
+        else:
+            aggregated = spmm_csr(crow, col, weights, x)
+            info = {"operation": "spmm", "choice": "native" if x.is_cuda else "baseline", "from_cache": False}
+        output = self.linear(aggregated)
+        return (output, info) if return_info else output

@@ -1,0 +1,446 @@
+// CSR row softmax and the fused SDDMM -> softmax -> SpMM attention row kernel for sm_100a.
+//
+// Reference behaviour (autosage/_auto.py:744-780): scores = SDDMM(Q, K); per CSR row
+// p = exp(s - max) / sum(exp(s - max)); out = SpMM(p, V).  The reference runs this as three passes
+// with about ten ATen kernels for the softmax alone and scores/probabilities round-tripping
+// through memory.
+//
+//   csr_softmax_kernel   the standalone softmax: one warp per light row, one CTA per hub row,
+//                        three sweeps over the row segment (max, sum, normalise).
+//   attention_kernel     the fused pipeline: for each 32-edge batch of a row the warp computes the
+//                        32 scores (same code as the SDDMM kernel), folds them into a running
+//                        maximum m and running sum l, rescales the output accumulator by
+//                        exp(m_old - m_new) and adds exp(s - m_new) * V[col]; hub rows are shared by
+//                        the warps of a CTA whose (m, l, acc) triples are merged at the end.
+//                        Scores and probabilities never leave registers.
+#include <math_constants.h>
+
+#include "asg_tile.cuh"
+
+namespace asg {
+
+// ------------------------------------------------------------------------------------ softmax
+struct SoftmaxArgs {
+  const int64_t* crow;
+  const float* scores;
+  float* probs;
+  Header* header;
+  const int* order;
+};
+
+__device__ __forceinline__ void softmax_segment_warp(const float* __restrict__ in, float* __restrict__ out,
+                                                     long long s, long long e, int lane) {
+  float m = -CUDART_INF_F;
+  for (long long p = s + lane; p < e; p += 32) m = fmaxf(m, in[p]);
+  m = warp_max(m);
+  float sum = 0.f;
+  for (long long p = s + lane; p < e; p += 32) sum += expf(in[p] - m);
+  sum = warp_sum(sum);
+  for (long long p = s + lane; p < e; p += 32) out[p] = expf(in[p] - m) / sum;
+}
+
+__global__ void __launch_bounds__(512) csr_softmax_kernel(const SoftmaxArgs a) {
+  __shared__ int s_item;
+  __shared__ float s_part[16];
+  __shared__ float s_bcast;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int n_warps = blockDim.x >> 5;
+  const int n_hub = a.header->n_hub;
+  const int n_light = a.header->n_light;
+
+  if (n_hub > 0) {
+    for (;;) {
+      __syncthreads();
+      if (tid == 0) {
+        const unsigned long long it = atomicAdd(&a.header->counter[0], 1ull);
+        s_item = it < static_cast<unsigned long long>(n_hub) ? static_cast<int>(it) : -1;
+      }
+      __syncthreads();
+      const int item = s_item;
+      if (item < 0) break;
+      const int row = a.order[item];
+      const long long s = a.crow[row];
+      const long long e = a.crow[row + 1];
+      float m = -CUDART_INF_F;
+      for (long long p = s + tid; p < e; p += blockDim.x) m = fmaxf(m, a.scores[p]);
+      m = warp_max(m);
+      if (lane == 0) s_part[warp] = m;
+      __syncthreads();
+      if (tid == 0) {
+        float t = s_part[0];
+        for (int w = 1; w < n_warps; ++w) t = fmaxf(t, s_part[w]);
+        s_bcast = t;
+      }
+      __syncthreads();
+      m = s_bcast;
+      float sum = 0.f;
+      for (long long p = s + tid; p < e; p += blockDim.x) sum += expf(a.scores[p] - m);
+      sum = warp_sum(sum);
+      __syncthreads();
+      if (lane == 0) s_part[warp] = sum;
+      __syncthreads();
+      if (tid == 0) {
+        float t = 0.f;
+        for (int w = 0; w < n_warps; ++w) t += s_part[w];
+        s_bcast = t;
+      }
+      __syncthreads();
+      sum = s_bcast;
+      for (long long p = s + tid; p < e; p += blockDim.x) a.probs[p] = expf(a.scores[p] - m) / sum;
+    }
+  }
+  if (n_light > 0) {
+    const int* light = a.order + n_hub;
+    for (;;) {
+      const unsigned long long it = warp_next(&a.header->counter[1]);
+      if (it >= static_cast<unsigned long long>(n_light)) break;
+      const int row = light[it];
+      softmax_segment_warp(a.scores, a.probs, a.crow[row], a.crow[row + 1], lane);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ fused attention
+struct AttentionArgs {
+  const int64_t* crow;
+  const int64_t* col;
+  const float* q;
+  const float* k;
+  const float* v;
+  float* out;
+  Header* header;
+  const int* order;
+  int f;
+  float scale;
+};
+
+// Online-softmax state of one warp for one row: running max m, running sum l and the output
+// accumulator (lane-group partial sums of the feature tile).
+template <int VW, int G, int NV, int U_REQUESTED>
+__device__ __forceinline__ void attention_batches(const AttentionArgs& a, int row, long long first, long long stride,
+                                                  int lane, uint64_t pol_keep, uint64_t pol_stream, float& m_run,
+                                                  float& l_run, float (&acc)[NV][VW]) {
+  constexpr int EPI = 32 / G;
+  constexpr int U = U_REQUESTED < G ? U_REQUESTED : G;  // an unrolled batch never exceeds 32 edges
+  constexpr int BU = EPI * U;
+  const int l = lane % G;
+  const int sub = lane / G;
+  const int f = a.f;
+  const long long e = a.crow[row + 1];
+  const float* qrow = a.q + static_cast<size_t>(row) * f;
+
+  float q[NV][VW];
+  bool fvalid[NV];
+  int foff[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    foff[v] = VW * (l + G * v);
+    fvalid[v] = foff[v] < f;
+    if (fvalid[v]) {
+      VecIO<VW>::load_plain(q[v], qrow + foff[v]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < VW; ++i) q[v][i] = 0.f;
+    }
+  }
+
+  for (long long p = first; p < e; p += stride) {
+    const int cnt = e - p < 32 ? static_cast<int>(e - p) : 32;
+    int c_l = 0;
+    if (lane < cnt) c_l = static_cast<int>(ld_index(a.col + p + lane, pol_stream));
+
+    // 1. scores of the batch: lane (l, sub) ends with the score of edge l*EPI + sub
+    float part[G];
+#pragma unroll
+    for (int i = 0; i < G; ++i) part[i] = 0.f;
+    batch_dots<VW, G, NV, U>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
+    const float dot = group_reduce_scatter<G>(part, l);
+    const int my_edge = l * EPI + sub;
+    const float score = my_edge < cnt ? dot * a.scale : -CUDART_INF_F;
+
+    // 2. fold into the running max / sum
+    const float m_new = fmaxf(m_run, warp_max(score));
+    const float rescale = expf(m_run - m_new);  // exp(-inf) = 0 on the first batch
+    const float prob = my_edge < cnt ? expf(score - m_new) : 0.f;
+    l_run = l_run * rescale + warp_sum(prob);
+    m_run = m_new;
+#pragma unroll
+    for (int v = 0; v < NV; ++v)
+#pragma unroll
+      for (int i = 0; i < VW; ++i) acc[v][i] *= rescale;
+
+    // 3. acc += sum_j prob_j * V[col_j]; the probability of edge j sits in lane (j/EPI) + G*(j%EPI)
+    for (int j = 0; j < cnt; j += BU) {
+      float xv[U][NV][VW];
+      float wu[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int src = j + u * EPI + sub;
+        const int c = __shfl_sync(kFull, c_l, src);
+        const float w = __shfl_sync(kFull, prob, (src / EPI) + G * (src % EPI));
+        const bool ok = src < cnt;
+        wu[u] = ok ? w : 0.f;
+        const float* vrow = a.v + static_cast<size_t>(c) * f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          if (ok && fvalid[v]) {
+            VecIO<VW>::load(xv[u][v], vrow + foff[v], pol_keep);
+          } else {
+#pragma unroll
+            for (int i = 0; i < VW; ++i) xv[u][v][i] = 0.f;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[v][i] = fmaf(wu[u], xv[u][v][i], acc[v][i]);
+    }
+  }
+}
+
+template <int VW, int G, int NV, int U>
+__global__ void __launch_bounds__(512) attention_kernel(const AttentionArgs a) {
+  constexpr int FT = VW * G * NV;
+  extern __shared__ __align__(16) unsigned char smem[];
+  int* s_item = reinterpret_cast<int*>(smem);
+  float* s_m = reinterpret_cast<float*>(smem + 16);   // [16]
+  float* s_l = s_m + 16;                               // [16]
+  float* s_acc = s_l + 16;                             // [n_warps][FT]
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int n_warps = blockDim.x >> 5;
+  const int l = lane % G;
+  const int sub = lane / G;
+  const uint64_t pol_keep = policy_evict_last();
+  const uint64_t pol_stream = policy_evict_first();
+  const int n_hub = a.header->n_hub;
+  const int n_light = a.header->n_light;
+  const int f = a.f;
+
+  if (n_hub > 0) {
+    for (;;) {
+      __syncthreads();
+      if (tid == 0) {
+        const unsigned long long it = atomicAdd(&a.header->counter[0], 1ull);
+        *s_item = it < static_cast<unsigned long long>(n_hub) ? static_cast<int>(it) : -1;
+      }
+      __syncthreads();
+      const int item = *s_item;
+      if (item < 0) break;
+      const int row = a.order[item];
+      float m_run = -CUDART_INF_F, l_run = 0.f;
+      float acc[NV][VW];
+#pragma unroll
+      for (int v = 0; v < NV; ++v)
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
+      attention_batches<VW, G, NV, U>(a, row, a.crow[row] + 32ll * warp, 32ll * n_warps, lane, pol_keep, pol_stream,
+                                      m_run, l_run, acc);
+#pragma unroll
+      for (int o = G; o < 32; o <<= 1)
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[v][i] += __shfl_xor_sync(kFull, acc[v][i], o);
+      if (lane == 0) {
+        s_m[warp] = m_run;
+        s_l[warp] = l_run;
+      }
+      if (sub == 0) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) s_acc[warp * FT + VW * (l + G * v) + i] = acc[v][i];
+      }
+      __syncthreads();
+      float m_all = s_m[0];
+      for (int w = 1; w < n_warps; ++w) m_all = fmaxf(m_all, s_m[w]);
+      float l_all = 0.f;
+      for (int w = 0; w < n_warps; ++w) l_all += s_l[w] * expf(s_m[w] - m_all);  // idle warps: 0 * exp(-inf) = 0
+      for (int i = tid; i < FT; i += blockDim.x) {
+        if (i < f) {
+          float t = 0.f;
+          for (int w = 0; w < n_warps; ++w) {
+            const float weight = s_l[w] > 0.f ? expf(s_m[w] - m_all) : 0.f;
+            t = fmaf(s_acc[w * FT + i], weight, t);
+          }
+          st_stream1(a.out + static_cast<size_t>(row) * f + i, l_all > 0.f ? t / l_all : 0.f);
+        }
+      }
+    }
+  }
+  if (n_light > 0) {
+    const int* light = a.order + n_hub;
+    for (;;) {
+      const unsigned long long it = warp_next(&a.header->counter[1]);
+      if (it >= static_cast<unsigned long long>(n_light)) break;
+      const int row = light[it];
+      float m_run = -CUDART_INF_F, l_run = 0.f;
+      float acc[NV][VW];
+#pragma unroll
+      for (int v = 0; v < NV; ++v)
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
+      attention_batches<VW, G, NV, U>(a, row, a.crow[row], 32ll, lane, pol_keep, pol_stream, m_run, l_run, acc);
+#pragma unroll
+      for (int o = G; o < 32; o <<= 1)
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[v][i] += __shfl_xor_sync(kFull, acc[v][i], o);
+      if (sub == 0) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          const int fo = VW * (l + G * v);
+          if (fo < f) {
+            float r[VW];
+#pragma unroll
+            for (int i = 0; i < VW; ++i) r[i] = acc[v][i] * inv;
+            VecIO<VW>::store(a.out + static_cast<size_t>(row) * f + fo, r);
+          }
+        }
+      }
+    }
+  }
+}
+
+template <int VW, int G, int NV, int U>
+static int launch_attention_instance(const AttentionArgs& args, int warps, cudaStream_t stream, int device) {
+  constexpr int FT = VW * G * NV;
+  auto kernel = attention_kernel<VW, G, NV, U>;
+  const int threads = warps * 32;
+  const size_t smem = 16 + 128 + size_t(4) * warps * FT;
+  if (smem > 48 * 1024)
+    ASG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  int per_sm = 0;
+  ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem));
+  if (per_sm < 1) per_sm = 1;
+  kernel<<<sm_count(device) * per_sm, threads, smem, stream>>>(args);
+  ASG_CUDA(cudaGetLastError());
+  return ASG_OK;
+}
+
+static bool aligned_to(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
+
+#ifndef ASG_ATTN_U
+#define ASG_ATTN_U 8
+#endif
+
+static int launch_attention(const AttentionArgs& args, int vw, int warps, cudaStream_t stream, int device) {
+  constexpr int U = ASG_ATTN_U;
+  const int f = args.f;
+  if (vw == 8) {
+    if (f <= 32) return launch_attention_instance<8, 4, 1, U / 2>(args, warps, stream, device);
+    if (f <= 64) return launch_attention_instance<8, 8, 1, U / 2>(args, warps, stream, device);
+    if (f <= 128) return launch_attention_instance<8, 16, 1, U / 2>(args, warps, stream, device);
+    if (f <= 256) return launch_attention_instance<8, 32, 1, U / 2>(args, warps, stream, device);
+    return launch_attention_instance<8, 32, 2, U / 4>(args, warps, stream, device);
+  }
+  if (vw == 4) {
+    if (f <= 32) return launch_attention_instance<4, 8, 1, U>(args, warps, stream, device);
+    if (f <= 64) return launch_attention_instance<4, 16, 1, U>(args, warps, stream, device);
+    if (f <= 128) return launch_attention_instance<4, 32, 1, U>(args, warps, stream, device);
+    if (f <= 256) return launch_attention_instance<4, 32, 2, U / 2>(args, warps, stream, device);
+    return launch_attention_instance<4, 32, 4, U / 4>(args, warps, stream, device);
+  }
+  if (f <= 32) return launch_attention_instance<1, 32, 1, U>(args, warps, stream, device);
+  if (f <= 64) return launch_attention_instance<1, 32, 2, U / 2>(args, warps, stream, device);
+  if (f <= 128) return launch_attention_instance<1, 32, 4, U / 4>(args, warps, stream, device);
+  if (f <= 256) return launch_attention_instance<1, 32, 8, U / 4>(args, warps, stream, device);
+  return launch_attention_instance<1, 32, 16, 1>(args, warps, stream, device);
+}
+
+}  // namespace asg
+
+extern "C" {
+
+int asg_csr_row_softmax(const int64_t* crow, const float* scores, float* probs, int64_t n_rows, int64_t nnz,
+                        int warps_per_block, int64_t hub_threshold, unsigned flags, void* workspace,
+                        size_t workspace_bytes, void* stream_ptr) {
+  using namespace asg;
+  ASG_REQUIRE(n_rows >= 0 && nnz >= 0, ASG_EINVAL, "sizes must be non-negative");
+  ASG_REQUIRE(n_rows <= 2147483647ll - 2048, ASG_ERANGE, "n_rows exceeds the kernel index range");
+  ASG_REQUIRE(warps_per_block == 2 || warps_per_block == 4 || warps_per_block == 8 || warps_per_block == 16,
+              ASG_EINVAL, "warps_per_block must be 2, 4, or 8");
+  if (n_rows == 0 || nnz == 0) return ASG_OK;
+  ASG_REQUIRE(crow != nullptr && scores != nullptr && probs != nullptr, ASG_EINVAL,
+              "crow, scores and probs must not be null");
+  if (int rc = check_workspace(workspace, workspace_bytes, n_rows)) return rc;
+  DeviceGuard guard(probs);
+  ASG_CUDA(guard.status);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (flags & ASG_FLAG_PLAN_READY) {
+    if (int rc = reset_counters(workspace, stream)) return rc;
+  } else {
+    if (int rc = plan_build(crow, n_rows, hub_threshold, workspace, stream)) return rc;
+  }
+  SoftmaxArgs args;
+  args.crow = crow;
+  args.scores = scores;
+  args.probs = probs;
+  args.header = static_cast<Header*>(workspace);
+  args.order = reinterpret_cast<const int*>(static_cast<const char*>(workspace) + order_offset());
+  const int threads = warps_per_block * 32;
+  int per_sm = 0;
+  ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, csr_softmax_kernel, threads, 0));
+  if (per_sm < 1) per_sm = 1;
+  csr_softmax_kernel<<<sm_count(guard.target) * per_sm, threads, 0, stream>>>(args);
+  ASG_CUDA(cudaGetLastError());
+  return ASG_OK;
+}
+
+int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, const float* k, const float* v,
+                      float* out, int64_t n_rows, int64_t nnz, int64_t f, float scale, int warps_per_block,
+                      int64_t hub_threshold, unsigned flags, void* workspace, size_t workspace_bytes,
+                      void* stream_ptr) {
+  using namespace asg;
+  ASG_REQUIRE(n_rows >= 0 && nnz >= 0 && f >= 0, ASG_EINVAL, "sizes must be non-negative");
+  ASG_REQUIRE(n_rows <= 2147483647ll - 2048, ASG_ERANGE, "n_rows exceeds the kernel index range");
+  ASG_REQUIRE(f <= 512, ASG_ERANGE, "the fused attention kernel holds at most 512 features per row");
+  ASG_REQUIRE(warps_per_block == 2 || warps_per_block == 4 || warps_per_block == 8 || warps_per_block == 16,
+              ASG_EINVAL, "warps_per_block must be 2, 4, or 8");
+  if (n_rows == 0 || f == 0) return ASG_OK;
+  ASG_REQUIRE(crow != nullptr && q != nullptr && k != nullptr && v != nullptr && out != nullptr, ASG_EINVAL,
+              "crow, query, key, value and out must not be null");
+  ASG_REQUIRE(nnz == 0 || col != nullptr, ASG_EINVAL, "col must not be null");
+  if (int rc = check_workspace(workspace, workspace_bytes, n_rows)) return rc;
+  DeviceGuard guard(out);
+  ASG_CUDA(guard.status);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (flags & ASG_FLAG_PLAN_READY) {
+    if (int rc = reset_counters(workspace, stream)) return rc;
+  } else {
+    if (int rc = plan_build(crow, n_rows, hub_threshold, workspace, stream)) return rc;
+  }
+  int vw = 1;
+  if (!(flags & ASG_FLAG_NO_VEC4)) {
+    const bool a32 = aligned_to(q, 32) && aligned_to(k, 32) && aligned_to(v, 32) && aligned_to(out, 32);
+    const bool a16 = aligned_to(q, 16) && aligned_to(k, 16) && aligned_to(v, 16) && aligned_to(out, 16);
+    if (f % 8 == 0 && a32) vw = 8;
+    else if (f % 4 == 0 && a16) vw = 4;
+  }
+#ifdef ASG_ATTN_MAX_VW
+  if (vw > ASG_ATTN_MAX_VW) vw = ASG_ATTN_MAX_VW;
+#endif
+  AttentionArgs args;
+  args.crow = crow;
+  args.col = col;
+  args.q = q;
+  args.k = k;
+  args.v = v;
+  args.out = out;
+  args.header = static_cast<Header*>(workspace);
+  args.order = reinterpret_cast<const int*>(static_cast<const char*>(workspace) + order_offset());
+  args.f = static_cast<int>(f);
+  args.scale = scale;
+  return launch_attention(args, vw, warps_per_block, stream, guard.target);
+}
+
+}  // extern "C"

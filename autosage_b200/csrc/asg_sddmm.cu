@@ -1,0 +1,235 @@
+// CSR SDDMM for sm_100a: out[e] = <Q[row(e), :], K[col[e], :]>.
+//
+// One persistent kernel, two work queues (see asg_plan.cu):
+//   queue 0  hub rows, one CTA each: the warps of the CTA take the row's 32-edge batches round-robin
+//   queue 1  light rows, one warp each
+// For a batch the warp loads 32 column indices with one coalesced load, keeps the Q row in
+// registers, gathers the K rows with vector loads (U instructions in flight per lane), and
+// turns the per-lane partial dot products into one finished value per lane with a
+// reduce-scatter (about one shuffle per edge instead of five), so the 32 results leave as one
+// coalesced 128-byte store.
+//
+// Replaces csrc/sddmm_csr_op.cu:19-83 of the reference (warp-per-row kernel with scalar loads, a
+// five-step shuffle reduction and a 4-byte store per edge; CTA-per-hub kernel of the same shape).
+#include "asg_tile.cuh"
+
+namespace asg {
+
+struct SddmmArgs {
+  const int64_t* crow;
+  const int64_t* col;
+  const float* q;
+  const float* k;
+  float* out;
+  Header* header;
+  const int* order;
+  int f;
+  int n_tiles;
+};
+
+template <int VW, int G, int NV, int U>
+__device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, long long first, long long stride,
+                                                  int lane, uint64_t pol_keep, uint64_t pol_stream) {
+  constexpr int EPI = 32 / G;
+  constexpr int FT = VW * G * NV;
+  const int l = lane % G;
+  const int sub = lane / G;
+  const int f = a.f;
+  const long long e = a.crow[row + 1];
+  const float* qrow = a.q + static_cast<size_t>(row) * f;
+
+  float q[NV][VW];
+  bool fvalid[NV];
+  int foff[NV];
+  auto load_q = [&](int tile) {
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      foff[v] = tile * FT + VW * (l + G * v);
+      fvalid[v] = foff[v] < f;
+      if (fvalid[v]) {
+        VecIO<VW>::load_plain(q[v], qrow + foff[v]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < VW; ++i) q[v][i] = 0.f;
+      }
+    }
+  };
+  if (a.n_tiles == 1) load_q(0);
+
+  for (long long p = first; p < e; p += stride) {
+    const int cnt = e - p < 32 ? static_cast<int>(e - p) : 32;
+    int c_l = 0;
+    if (lane < cnt) c_l = static_cast<int>(ld_index(a.col + p + lane, pol_stream));
+    float part[G];
+#pragma unroll
+    for (int i = 0; i < G; ++i) part[i] = 0.f;
+    if (a.n_tiles == 1) {
+      batch_dots<VW, G, NV, U>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
+    } else {
+      for (int tile = 0; tile < a.n_tiles; ++tile) {
+        load_q(tile);
+        batch_dots<VW, G, NV, U>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
+      }
+    }
+    const float dot = group_reduce_scatter<G>(part, l);
+    const int edge = l * EPI + sub;
+    if (edge < cnt) st_stream1(a.out + p + edge, dot);
+  }
+}
+
+template <int VW, int G, int NV, int U>
+__global__ void __launch_bounds__(512) sddmm_kernel(const SddmmArgs a) {
+  __shared__ int s_item;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int n_warps = blockDim.x >> 5;
+  const uint64_t pol_keep = policy_evict_last();
+  const uint64_t pol_stream = policy_evict_first();
+  const int n_hub = a.header->n_hub;
+  const int n_light = a.header->n_light;
+
+  if (n_hub > 0) {
+    for (;;) {
+      __syncthreads();
+      if (tid == 0) {
+        const unsigned long long it = atomicAdd(&a.header->counter[0], 1ull);
+        s_item = it < static_cast<unsigned long long>(n_hub) ? static_cast<int>(it) : -1;
+      }
+      __syncthreads();
+      const int item = s_item;
+      if (item < 0) break;
+      const int row = a.order[item];
+      const long long s = a.crow[row];
+      sddmm_row_batches<VW, G, NV, U>(a, row, s + 32ll * warp, 32ll * n_warps, lane, pol_keep, pol_stream);
+    }
+  }
+  if (n_light > 0) {
+    const int* light = a.order + n_hub;
+    for (;;) {
+      const unsigned long long it = warp_next(&a.header->counter[1]);
+      if (it >= static_cast<unsigned long long>(n_light)) break;
+      const int row = light[it];
+      sddmm_row_batches<VW, G, NV, U>(a, row, a.crow[row], 32ll, lane, pol_keep, pol_stream);
+    }
+  }
+}
+
+template <int VW, int G, int NV, int U>
+static int launch_instance(const SddmmArgs& args, int warps, cudaStream_t stream, int device) {
+  auto kernel = sddmm_kernel<VW, G, NV, U>;
+  const int threads = warps * 32;
+  int per_sm = 0;
+  ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
+  if (per_sm < 1) per_sm = 1;
+  kernel<<<sm_count(device) * per_sm, threads, 0, stream>>>(args);
+  ASG_CUDA(cudaGetLastError());
+  return ASG_OK;
+}
+
+#ifndef ASG_SDDMM_U
+#define ASG_SDDMM_U 8
+#endif
+
+// Picks the narrowest tile that covers f (so Q stays in registers); above 512 floats the tile is
+// 512 wide and Q is re-read per batch.
+static int launch_sddmm(SddmmArgs& args, int vw, cudaStream_t stream, int warps, int device) {
+  constexpr int U = ASG_SDDMM_U;
+  const int f = args.f;
+  auto tiles = [&](int ft) { args.n_tiles = (f + ft - 1) / ft; };
+  if (vw == 8) {
+    if (f <= 32) { tiles(32); return launch_instance<8, 4, 1, U / 2>(args, warps, stream, device); }
+    if (f <= 64) { tiles(64); return launch_instance<8, 8, 1, U / 2>(args, warps, stream, device); }
+    if (f <= 128) { tiles(128); return launch_instance<8, 16, 1, U / 2>(args, warps, stream, device); }
+    if (f <= 256) { tiles(256); return launch_instance<8, 32, 1, U / 2>(args, warps, stream, device); }
+    tiles(512);
+    return launch_instance<8, 32, 2, U / 4>(args, warps, stream, device);
+  }
+  if (vw == 4) {
+    if (f <= 32) { tiles(32); return launch_instance<4, 8, 1, U>(args, warps, stream, device); }
+    if (f <= 64) { tiles(64); return launch_instance<4, 16, 1, U>(args, warps, stream, device); }
+    if (f <= 128) { tiles(128); return launch_instance<4, 32, 1, U>(args, warps, stream, device); }
+    if (f <= 256) { tiles(256); return launch_instance<4, 32, 2, U / 2>(args, warps, stream, device); }
+    tiles(512);
+    return launch_instance<4, 32, 4, U / 4>(args, warps, stream, device);
+  }
+  if (f <= 32) { tiles(32); return launch_instance<1, 32, 1, U>(args, warps, stream, device); }
+  if (f <= 64) { tiles(64); return launch_instance<1, 32, 2, U / 2>(args, warps, stream, device); }
+  tiles(128);
+  return launch_instance<1, 32, 4, U / 4>(args, warps, stream, device);
+}
+
+static bool aligned_to(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
+
+static int sddmm_entry(const int64_t* crow, const int64_t* col, const float* q, const float* k, float* out,
+                       int64_t n_rows, int64_t nnz, int64_t f, int warps, int64_t hub_threshold, unsigned flags,
+                       void* workspace, size_t workspace_bytes, void* stream_ptr) {
+  ASG_REQUIRE(n_rows >= 0 && nnz >= 0 && f >= 0, ASG_EINVAL, "sizes must be non-negative");
+  ASG_REQUIRE(n_rows <= 2147483647ll - 2048 && f <= 2147483647ll, ASG_ERANGE,
+              "SDDMM dimensions exceed the kernel index range");
+  ASG_REQUIRE(warps == 2 || warps == 4 || warps == 8 || warps == 16, ASG_EINVAL,
+              "warps_per_block must be 2, 4, or 8");
+  ASG_REQUIRE(!(flags & ASG_FLAG_ACCUMULATE), ASG_EINVAL, "SDDMM does not accumulate");
+  if (n_rows == 0 || nnz == 0) return ASG_OK;
+  ASG_REQUIRE(crow != nullptr && col != nullptr && out != nullptr, ASG_EINVAL, "crow, col and out must not be null");
+  ASG_REQUIRE(f == 0 || (q != nullptr && k != nullptr), ASG_EINVAL, "query and key must not be null");
+  if (int rc = check_workspace(workspace, workspace_bytes, n_rows)) return rc;
+  DeviceGuard guard(out);
+  ASG_CUDA(guard.status);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  if (f == 0) {
+    ASG_CUDA(cudaMemsetAsync(out, 0, size_t(4) * size_t(nnz), stream));
+    return ASG_OK;
+  }
+  if (flags & ASG_FLAG_PLAN_READY) {
+    if (int rc = reset_counters(workspace, stream)) return rc;
+  } else {
+    if (int rc = plan_build(crow, n_rows, hub_threshold, workspace, stream)) return rc;
+  }
+  int vw = 1;
+  if (!(flags & ASG_FLAG_NO_VEC4)) {
+    if (f % 8 == 0 && aligned_to(q, 32) && aligned_to(k, 32)) vw = 8;
+    else if (f % 4 == 0 && aligned_to(q, 16) && aligned_to(k, 16)) vw = 4;
+  }
+#ifdef ASG_SDDMM_MAX_VW
+  if (vw > ASG_SDDMM_MAX_VW) vw = ASG_SDDMM_MAX_VW;
+#endif
+  SddmmArgs args;
+  args.crow = crow;
+  args.col = col;
+  args.q = q;
+  args.k = k;
+  args.out = out;
+  args.header = static_cast<Header*>(workspace);
+  args.order = reinterpret_cast<const int*>(static_cast<const char*>(workspace) + order_offset());
+  args.f = static_cast<int>(f);
+  args.n_tiles = 1;
+  return launch_sddmm(args, vw, stream, warps, guard.target);
+}
+
+}  // namespace asg
+
+extern "C" {
+
+int asg_sddmm_csr_ex(const int64_t* crow, const int64_t* col, const float* q, const float* k, float* out,
+                     int64_t n_rows, int64_t nnz, int64_t f, int warps_per_block, int64_t hub_threshold,
+                     unsigned flags, void* workspace, size_t workspace_bytes, void* stream) {
+  return asg::sddmm_entry(crow, col, q, k, out, n_rows, nnz, f, warps_per_block, hub_threshold, flags, workspace,
+                          workspace_bytes, stream);
+}
+
+int asg_sddmm_csr_split(const int64_t* crow, const int64_t* col, const float* q, const float* k, float* out,
+                        int64_t n_rows, int64_t nnz, int64_t f, int warps_per_block, int64_t hub_threshold,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  if (hub_threshold <= 0 || hub_threshold > 2147483647ll)
+    return asg::fail(ASG_EINVAL, "%s", "hub_threshold must be a positive 32-bit integer");
+  return asg::sddmm_entry(crow, col, q, k, out, n_rows, nnz, f, warps_per_block, hub_threshold, 0u, workspace,
+                          workspace_bytes, stream);
+}
+
+int asg_sddmm_csr(const int64_t* crow, const int64_t* col, const float* q, const float* k, float* out,
+                  int64_t n_rows, int64_t nnz, int64_t f, void* workspace, size_t workspace_bytes, void* stream) {
+  return asg::sddmm_entry(crow, col, q, k, out, n_rows, nnz, f, 8, 2048, 0u, workspace, workspace_bytes, stream);
+}
+
+}  // extern "C"

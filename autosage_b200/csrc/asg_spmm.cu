@@ -1,0 +1,471 @@
+// CSR SpMM for sm_100a: one persistent kernel that drains two work queues built by the plan.
+//
+//   queue 0  hub rows (degree >= threshold): one CTA per (hub row, feature tile).  The row's
+//            col/val segment is staged into shared memory in chunks by 1-D bulk async copies (TMA
+//            without a tensor map, mbarrier completion, two stages); every warp of the CTA then
+//            gathers rows of X for its share of the chunk and the per-warp partial sums are
+//            combined through shared memory.
+//   queue 1  light rows: one warp per (row, feature tile).  col/val are fetched 32 edges at a time
+//            with one coalesced load per lane and broadcast by shuffles; X rows are gathered with
+//            scalar, 128-bit or 256-bit loads, U load instructions in flight per lane.
+//
+// Items are ordered tile-major (all rows for tile 0, then tile 1, ...) so that, when X is larger
+// than L2, the part of X being gathered at any time is N x FT floats only.
+//
+// Replaces csrc/spmm_csr_vec4.cu:23-89 (scalar and vec4 warp-per-row kernels),
+// csrc/spmm_rows.cu:11-81 (row-list kernel) and csrc/spmm_hub.cu:13-93 (CTA-per-hub kernel) of the
+// reference.  Offsets into X and Y are 64-bit (the reference multiplies 32-bit ints).
+#include "asg_tile.cuh"
+
+namespace asg {
+
+struct SpmmArgs {
+  const int64_t* crow;
+  const int64_t* col;
+  const float* val;
+  const float* x;
+  float* y;
+  Header* header;
+  const int* order;
+  int f;
+  int n_tiles;
+  int accumulate;
+  int bulk_stage;
+};
+
+constexpr int kChunkPerWarp = 128;  // staged edges per warp and stage in the hub path
+
+template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL>
+__global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
+  constexpr int U = U_REQUESTED < G ? U_REQUESTED : G;  // an unrolled batch never exceeds 32 edges
+  constexpr int EPI = 32 / G;          // edges per load instruction
+  constexpr int FT = VW * G * NV;      // feature tile
+  constexpr int BU = EPI * U;          // edges per unrolled batch
+  static_assert(32 % BU == 0, "batch must divide a 32-edge chunk");
+
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int n_warps = blockDim.x >> 5;
+  const int l = lane % G;
+  const int sub = lane / G;
+  const int chunk = kChunkPerWarp * n_warps;
+
+  // shared memory carve-up
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                       // 2 mbarriers
+  int* s_item = reinterpret_cast<int*>(smem + 16);                          // CTA-wide item id
+  long long* s_col = reinterpret_cast<long long*>(smem + 128);              // [2][chunk]
+  float* s_val = reinterpret_cast<float*>(smem + 128 + size_t(16) * chunk); // [2][chunk]
+  float* s_red = reinterpret_cast<float*>(smem + 128 + size_t(24) * chunk); // [n_warps][FT]
+
+  const uint64_t pol_keep = policy_evict_last();
+  const uint64_t pol_stream = policy_evict_first();
+  const int f = a.f;
+  const int n_hub = a.header->n_hub;
+  const int n_light = a.header->n_light;
+
+  // ------------------------------------------------------------------ queue 0: hub rows
+  if (n_hub > 0) {
+    if (tid == 0) {
+      mbar_init(&bars[0], 1);
+      mbar_init(&bars[1], 1);
+      mbar_fence_init();
+    }
+    unsigned seq = 0;  // chunks staged so far by this CTA: stage = seq & 1, parity = (seq >> 1) & 1
+    const long long total = static_cast<long long>(n_hub) * a.n_tiles;
+    bool alive = true;
+    while (alive) {
+      __syncthreads();
+      if (tid == 0) {
+        const unsigned long long it = atomicAdd(&a.header->counter[0], 1ull);
+        *s_item = it < static_cast<unsigned long long>(total) ? static_cast<int>(it) : -1;
+      }
+      __syncthreads();
+      const int item = *s_item;
+      if (item < 0) break;
+      const int tile = item / n_hub;
+      const int row = a.order[item - tile * n_hub];
+      const int fbase = tile * FT;
+      const long long s = a.crow[row];
+      const long long e = a.crow[row + 1];
+      const long long a0 = s & ~3ll;  // staging starts on a 4-edge boundary (32 B of col, 16 B of val)
+      const int n_chunks = static_cast<int>((e - a0 + chunk - 1) / chunk);
+
+      float acc[NV][VW];
+#pragma unroll
+      for (int v = 0; v < NV; ++v)
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
+      bool fvalid[NV];
+      int foff[NV];
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        foff[v] = fbase + VW * (l + G * v);
+        fvalid[v] = foff[v] < f;
+      }
+
+      // stage one chunk [g0, g1) of col/val into stage `st`
+      auto stage_chunk = [&](int k, unsigned sq) {
+        const int st = sq & 1;
+        const long long g0 = a0 + static_cast<long long>(k) * chunk;
+        const long long g1 = g0 + chunk < e ? g0 + chunk : e;
+        const int count = static_cast<int>(g1 - g0);
+        long long* dcol = s_col + st * chunk;
+        float* dval = s_val + st * chunk;
+        if (a.bulk_stage) {
+          const int body = count & ~3;
+          if (tid == 0) {
+            const unsigned bytes = static_cast<unsigned>(body) * (HAS_VAL ? 12u : 8u);
+            mbar_expect_tx(&bars[st], bytes);
+            if (body > 0) {
+              bulk_g2s(dcol, a.col + g0, static_cast<unsigned>(body) * 8u, &bars[st]);
+              if (HAS_VAL) bulk_g2s(dval, a.val + g0, static_cast<unsigned>(body) * 4u, &bars[st]);
+            }
+          }
+          if (tid < count - body) {
+            dcol[body + tid] = a.col[g0 + body + tid];
+            if (HAS_VAL) dval[body + tid] = a.val[g0 + body + tid];
+          }
+        } else {
+          for (int i = tid; i < count; i += blockDim.x) {
+            dcol[i] = ld_index(a.col + g0 + i, pol_stream);
+            if (HAS_VAL) dval[i] = ld_weight(a.val + g0 + i, pol_stream);
+          }
+        }
+      };
+
+      if (n_chunks > 0) stage_chunk(0, seq);
+      __syncthreads();
+      // Every thread runs every iteration (the barriers below are CTA-wide); a thread whose
+      // bounded wait expired stops consuming and the CTA leaves together after the loop.
+      for (int k = 0; k < n_chunks; ++k) {
+        if (k + 1 < n_chunks) stage_chunk(k + 1, seq + 1);
+        const int st = seq & 1;
+        if (a.bulk_stage && alive) {
+          if (!mbar_wait_bounded(&bars[st], (seq >> 1) & 1)) {
+            atomicCAS(&a.header->status, 0, kStatusBulkWaitExpired);
+            alive = false;
+          }
+        }
+        if (alive) {
+          const long long g0 = a0 + static_cast<long long>(k) * chunk;
+          const long long g1 = g0 + chunk < e ? g0 + chunk : e;
+          const long long lo = g0 > s ? g0 : s;
+          const int base = static_cast<int>(lo - g0);
+          const int cnt = static_cast<int>(g1 - lo);
+          const long long* ccol = s_col + st * chunk + base;
+          const float* cval = s_val + st * chunk + base;
+          const int n_batches = (cnt + BU - 1) / BU;
+          for (int b = warp; b < n_batches; b += n_warps) {
+            float xv[U][NV][VW];
+            float wu[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int j = b * BU + u * EPI + sub;
+              const bool ok = j < cnt;
+              long long c = 0;
+              wu[u] = 0.f;
+              if (ok) {
+                c = ccol[j];
+                wu[u] = HAS_VAL ? cval[j] : 1.f;
+              }
+              const float* xrow = a.x + static_cast<size_t>(c) * f;
+#pragma unroll
+              for (int v = 0; v < NV; ++v) {
+                if (ok && fvalid[v]) {
+                  VecIO<VW>::load(xv[u][v], xrow + foff[v], pol_keep);
+                } else {
+#pragma unroll
+                  for (int i = 0; i < VW; ++i) xv[u][v][i] = 0.f;
+                }
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+              for (int v = 0; v < NV; ++v)
+#pragma unroll
+                for (int i = 0; i < VW; ++i) acc[v][i] = fmaf(wu[u], xv[u][v][i], acc[v][i]);
+          }
+        }
+        ++seq;
+        // All warps have finished reading this stage (and the plain-store tail of the next stage
+        // is visible) before the stage is refilled.
+        if (a.bulk_stage) fence_proxy_async();
+        __syncthreads();
+      }
+      // a bounded wait gave up in some thread: every thread leaves together, after one more
+      // bounded wait for the copies that may still be in flight into this CTA's shared memory
+      if (__syncthreads_or(!alive)) {
+        if (tid == 0 && a.bulk_stage && seq > 0) mbar_wait_bounded(&bars[(seq - 1) & 1], ((seq - 1) >> 1) & 1);
+        alive = false;
+        break;
+      }
+
+      // combine lane groups, then warps
+#pragma unroll
+      for (int o = G; o < 32; o <<= 1)
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[v][i] += __shfl_xor_sync(kFull, acc[v][i], o);
+      if (sub == 0) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) s_red[warp * FT + VW * (l + G * v) + i] = acc[v][i];
+      }
+      __syncthreads();
+      for (int i = tid; i < FT; i += blockDim.x) {
+        if (fbase + i < f) {
+          float total_i = 0.f;
+          for (int w = 0; w < n_warps; ++w) total_i += s_red[w * FT + i];
+          float* dst = a.y + static_cast<size_t>(row) * f + fbase + i;
+          if (a.accumulate) total_i += *dst;
+          st_stream1(dst, total_i);
+        }
+      }
+    }
+    if (!alive) return;
+  }
+
+  // ------------------------------------------------------------------ queue 1: light rows
+  if (n_light > 0) {
+    const long long total = static_cast<long long>(n_light) * a.n_tiles;
+    const int* light = a.order + n_hub;
+    for (;;) {
+      const unsigned long long it = warp_next(&a.header->counter[1]);
+      if (it >= static_cast<unsigned long long>(total)) break;
+      const int tile = static_cast<int>(it / n_light);
+      const int row = light[it - static_cast<unsigned long long>(tile) * n_light];
+      const int fbase = tile * FT;
+      const long long s = a.crow[row];
+      const long long e = a.crow[row + 1];
+
+      float acc[NV][VW];
+#pragma unroll
+      for (int v = 0; v < NV; ++v)
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
+      bool fvalid[NV];
+      int foff[NV];
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        foff[v] = fbase + VW * (l + G * v);
+        fvalid[v] = foff[v] < f;
+      }
+
+      int c_next = 0;
+      float w_next = 0.f;
+      if (s + lane < e) {
+        c_next = static_cast<int>(ld_index(a.col + s + lane, pol_stream));
+        if (HAS_VAL) w_next = ld_weight(a.val + s + lane, pol_stream);
+      }
+      for (long long p = s; p < e; p += 32) {
+        const int c_l = c_next;
+        const float w_l = w_next;
+        const int cnt = e - p < 32 ? static_cast<int>(e - p) : 32;
+        if (p + 32 + lane < e) {
+          c_next = static_cast<int>(ld_index(a.col + p + 32 + lane, pol_stream));
+          if (HAS_VAL) w_next = ld_weight(a.val + p + 32 + lane, pol_stream);
+        }
+        for (int j = 0; j < cnt; j += BU) {
+          float xv[U][NV][VW];
+          float wu[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int src = j + u * EPI + sub;
+            const int c = __shfl_sync(kFull, c_l, src);
+            if (HAS_VAL) wu[u] = __shfl_sync(kFull, w_l, src);
+            const bool ok = src < cnt;
+            if (!HAS_VAL) wu[u] = ok ? 1.f : 0.f;
+            if (HAS_VAL && !ok) wu[u] = 0.f;
+            const float* xrow = a.x + static_cast<size_t>(c) * f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+              if (ok && fvalid[v]) {
+                VecIO<VW>::load(xv[u][v], xrow + foff[v], pol_keep);
+              } else {
+#pragma unroll
+                for (int i = 0; i < VW; ++i) xv[u][v][i] = 0.f;
+              }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+              for (int i = 0; i < VW; ++i) acc[v][i] = fmaf(wu[u], xv[u][v][i], acc[v][i]);
+        }
+      }
+#pragma unroll
+      for (int o = G; o < 32; o <<= 1)
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[v][i] += __shfl_xor_sync(kFull, acc[v][i], o);
+      if (sub == 0) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          if (fvalid[v]) {
+            float* dst = a.y + static_cast<size_t>(row) * f + foff[v];
+            if (a.accumulate) {
+              float old[VW];
+              VecIO<VW>::load_plain(old, dst);
+#pragma unroll
+              for (int i = 0; i < VW; ++i) acc[v][i] += old[i];
+            }
+            VecIO<VW>::store(dst, acc[v]);
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+template <int VW, int G, int NV, int U, bool HAS_VAL>
+static int launch_instance(const SpmmArgs& args, int warps, cudaStream_t stream, int device) {
+  constexpr int FT = VW * G * NV;
+  auto kernel = spmm_kernel<VW, G, NV, U, HAS_VAL>;
+  const int threads = warps * 32;
+  const int chunk = kChunkPerWarp * warps;
+  const size_t smem = 128 + size_t(24) * chunk + size_t(4) * warps * FT;
+  if (smem > 48 * 1024) {
+    ASG_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  }
+  int per_sm = 0;
+  ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem));
+  if (per_sm < 1) per_sm = 1;
+  const int grid = sm_count(device) * per_sm;
+  kernel<<<grid, threads, smem, stream>>>(args);
+  ASG_CUDA(cudaGetLastError());
+  return ASG_OK;
+}
+
+template <int VW, int G, int NV, int U>
+static int launch_val(const SpmmArgs& args, int warps, cudaStream_t stream, int device) {
+  if (args.val != nullptr) return launch_instance<VW, G, NV, U, true>(args, warps, stream, device);
+  return launch_instance<VW, G, NV, U, false>(args, warps, stream, device);
+}
+
+#ifndef ASG_SPMM_U4
+#define ASG_SPMM_U4 8  // load instructions in flight per lane, 128-bit loads
+#endif
+#ifndef ASG_SPMM_U8
+#define ASG_SPMM_U8 4  // 256-bit loads
+#endif
+#ifndef ASG_SPMM_U1
+#define ASG_SPMM_U1 4  // scalar loads (times FT/32 loads each)
+#endif
+
+static int launch_spmm(const SpmmArgs& args, int vw, int feature_tile, int warps, cudaStream_t stream, int device) {
+  constexpr int U4 = ASG_SPMM_U4, U8 = ASG_SPMM_U8, U1 = ASG_SPMM_U1;
+  if (vw == 8) {
+    switch (feature_tile) {
+      case 32: return launch_val<8, 4, 1, U8>(args, warps, stream, device);
+      case 64: return launch_val<8, 8, 1, U8>(args, warps, stream, device);
+      case 128: return launch_val<8, 16, 1, (U8 > 2 ? U8 : 2)>(args, warps, stream, device);
+      default: return launch_val<8, 32, 1, U8>(args, warps, stream, device);
+    }
+  }
+  if (vw == 4) {
+    switch (feature_tile) {
+      case 32: return launch_val<4, 8, 1, U4>(args, warps, stream, device);
+      case 64: return launch_val<4, 16, 1, U4>(args, warps, stream, device);
+      case 128: return launch_val<4, 32, 1, U4>(args, warps, stream, device);
+      default: return launch_val<4, 32, 2, (U4 > 4 ? U4 / 2 : U4)>(args, warps, stream, device);
+    }
+  }
+  switch (feature_tile) {
+    case 32: return launch_val<1, 32, 1, U1 * 2>(args, warps, stream, device);
+    case 64: return launch_val<1, 32, 2, U1>(args, warps, stream, device);
+    case 128: return launch_val<1, 32, 4, U1>(args, warps, stream, device);
+    default: return launch_val<1, 32, 8, (U1 > 2 ? U1 / 2 : U1)>(args, warps, stream, device);
+  }
+}
+
+static bool aligned_to(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
+
+static int spmm_entry(const int64_t* crow, const int64_t* col, const float* val, const float* x, float* y,
+                      int64_t n_rows, int64_t nnz, int64_t f, int feature_tile, int warps, int64_t hub_threshold,
+                      unsigned flags, void* workspace, size_t workspace_bytes, void* stream_ptr) {
+  ASG_REQUIRE(n_rows >= 0 && nnz >= 0 && f >= 0, ASG_EINVAL, "sizes must be non-negative");
+  ASG_REQUIRE(n_rows <= 2147483647ll - 2048 && f <= 2147483647ll, ASG_ERANGE,
+              "SpMM dimensions exceed the kernel index range");
+  ASG_REQUIRE(feature_tile == 32 || feature_tile == 64 || feature_tile == 128 || feature_tile == 256, ASG_EINVAL,
+              "feature_tile must be 64 or 128");
+  ASG_REQUIRE(warps == 2 || warps == 4 || warps == 8 || warps == 16, ASG_EINVAL,
+              "warps_per_block must be 2, 4, or 8");
+  if (n_rows == 0 || f == 0) return ASG_OK;
+  ASG_REQUIRE(crow != nullptr && x != nullptr && y != nullptr, ASG_EINVAL, "crow, x and y must not be null");
+  ASG_REQUIRE(nnz == 0 || col != nullptr, ASG_EINVAL, "col must not be null");
+  if (int rc = check_workspace(workspace, workspace_bytes, n_rows)) return rc;
+  DeviceGuard guard(x);
+  ASG_CUDA(guard.status);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+
+  if (flags & ASG_FLAG_PLAN_READY) {
+    if (int rc = reset_counters(workspace, stream)) return rc;
+  } else {
+    if (int rc = plan_build(crow, n_rows, hub_threshold, workspace, stream)) return rc;
+  }
+
+  int vw = 1;
+  if (!(flags & ASG_FLAG_NO_VEC4)) {
+    if (f % 8 == 0 && aligned_to(x, 32) && aligned_to(y, 32)) vw = 8;
+    else if (f % 4 == 0 && aligned_to(x, 16) && aligned_to(y, 16)) vw = 4;
+  }
+#ifdef ASG_SPMM_MAX_VW
+  if (vw > ASG_SPMM_MAX_VW) vw = ASG_SPMM_MAX_VW;
+#endif
+  // a tile wider than the (rounded-up) feature count only wastes lanes
+  while (feature_tile > 32 && feature_tile / 2 >= f) feature_tile /= 2;
+
+  SpmmArgs args;
+  args.crow = crow;
+  args.col = col;
+  args.val = val;
+  args.x = x;
+  args.y = y;
+  args.header = static_cast<Header*>(workspace);
+  args.order = reinterpret_cast<const int*>(static_cast<const char*>(workspace) + order_offset());
+  args.f = static_cast<int>(f);
+  args.n_tiles = static_cast<int>((f + feature_tile - 1) / feature_tile);
+  args.accumulate = (flags & ASG_FLAG_ACCUMULATE) ? 1 : 0;
+  args.bulk_stage = (!(flags & ASG_FLAG_NO_BULK_STAGE) && aligned_to(col, 16) && (val == nullptr || aligned_to(val, 16))) ? 1 : 0;
+  return launch_spmm(args, vw, feature_tile, warps, stream, guard.target);
+}
+
+}  // namespace asg
+
+extern "C" {
+
+int asg_spmm_csr_ex(const int64_t* crow, const int64_t* col, const float* val, const float* x, float* y,
+                    int64_t n_rows, int64_t nnz, int64_t f, int feature_tile, int warps_per_block,
+                    int64_t hub_threshold, unsigned flags, void* workspace, size_t workspace_bytes, void* stream) {
+  return asg::spmm_entry(crow, col, val, x, y, n_rows, nnz, f, feature_tile, warps_per_block, hub_threshold, flags,
+                         workspace, workspace_bytes, stream);
+}
+
+int asg_spmm_csr_split(const int64_t* crow, const int64_t* col, const float* val, const float* x, float* y,
+                       int64_t n_rows, int64_t nnz, int64_t f, int feature_tile, int warps_per_block,
+                       int64_t hub_threshold, void* workspace, size_t workspace_bytes, void* stream) {
+  if (hub_threshold <= 0) return asg::fail(ASG_EINVAL, "%s", "hub_threshold must be positive");
+  return asg::spmm_entry(crow, col, val, x, y, n_rows, nnz, f, feature_tile, warps_per_block, hub_threshold, 0u,
+                         workspace, workspace_bytes, stream);
+}
+
+int asg_spmm_csr(const int64_t* crow, const int64_t* col, const float* val, const float* x, float* y,
+                 int64_t n_rows, int64_t nnz, int64_t f, void* workspace, size_t workspace_bytes, void* stream) {
+  // Defaults: 128-wide tiles (64 when the rows are that narrow), 8 warps, hubs from 2048 edges up.
+  const int tile = f <= 64 ? 64 : 128;
+  return asg::spmm_entry(crow, col, val, x, y, n_rows, nnz, f, tile, 8, 2048, 0u, workspace, workspace_bytes,
+                         stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,454 @@
+"""Benchmark of the sparse hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c2_spmm|c3_sddmm|c4_attention|c5_spmm] [--features F]
+
+One "step" is one pass of the hot path (one SpMM / SDDMM / attention call) over the whole synthetic
+graph.  Metric: algorithmic GB/s (bytes = CSR + gathered dense rows + output, the byte model of the
+roofline) with edges*F/s alongside.  N = 1 runs BASELINE configuration 2 (232,965 rows, ~114.6 M
+nnz, weighted, F = 128); N > 1 shards the rows of configuration 5 (2,449,029 rows, ~123.7 M nnz)
+by nnz over the ranks, all-gathers X over NCCL inside the timed region and reports strong scaling.
+
+The line printed by rank 0 carries, beside the contract keys:
+  roofline      achieved algorithmic GB/s of the dominant kernel against the measured HBM copy peak
+  cpu_baseline  the reference's CPU path (torch.sparse.mm over a CSR tensor, restated in oracle/)
+                timed on this host on a bounded row sample of the same workload
+  e2e           the same metric through the public API with HOST buffers (pinned), H2D and D2H
+                copies inside the timed region
+  clocks        SM clock and throttle reasons sampled during the timed region
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+# ------------------------------------------------------------------------------------------------
+def measured_peak() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    try:
+        value = float(json.loads(path.read_text())["hbm_gbs"])
+        return value, "measured"
+    except (OSError, ValueError, KeyError):
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+def spmm_bytes(n_rows: int, nnz: int, f: int, weighted: bool) -> int:
+    """CSR + gathered X + output: 8(N+1) + 8 nnz [+ 4 nnz] + 4 nnz F + 4 N F."""
+    return 8 * (n_rows + 1) + 8 * nnz + (4 * nnz if weighted else 0) + 4 * nnz * f + 4 * n_rows * f
+
+
+def sddmm_bytes(n_rows: int, nnz: int, f: int) -> int:
+    return 8 * (n_rows + 1) + 8 * nnz + 4 * n_rows * f + 4 * nnz * f + 4 * nnz
+
+
+def attention_bytes(n_rows: int, nnz: int, f: int) -> int:
+    return 8 * (n_rows + 1) + 8 * nnz + 4 * n_rows * f + 2 * 4 * nnz * f + 4 * n_rows * f
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int) -> None:
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._handle = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:  # NVML missing: report nulls
+            self._handle = None
+
+    def _loop(self) -> None:
+        nv = self._nvml
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)))
+                getter = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(
+                    nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+                mask = int(getter(self._handle))
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self._handle is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline (the reference's CPU path, restated in oracle/) on a bounded row sample
+# ------------------------------------------------------------------------------------------------
+def cpu_spmm_sample(crow_cpu, col_cpu, val_cpu, x_cpu, target_nnz: int, repeats: int):
+    """Times torch.sparse.mm over the first rows holding ~target_nnz edges (all columns kept, so
+    the gather pattern over X is the full workload's).  Returns (seconds per call, rows, nnz)."""
+    from oracle import oracle
+
+    rows = int(torch.searchsorted(crow_cpu, torch.tensor(target_nnz)).clamp(1, crow_cpu.numel() - 1))
+    sub_crow = crow_cpu[: rows + 1].contiguous()
+    nnz = int(sub_crow[-1])
+    sub_col = col_cpu[:nnz].contiguous()
+    sub_val = None if val_cpu is None else val_cpu[:nnz].contiguous()
+    times = []
+    for _ in range(repeats + 1):
+        t0 = time.perf_counter()
+        oracle.spmm_reference_cpu(sub_crow, sub_col, sub_val, x_cpu)
+        times.append(time.perf_counter() - t0)
+    return min(times[1:]) if len(times) > 1 else times[0], rows, nnz
+
+
+# ------------------------------------------------------------------------------------------------
+def build_workload(name: str, f: int, device):
+    from autosage_b200 import synthetic as syn
+
+    spec = {"c2_spmm": syn.REDDIT_LIKE, "c3_sddmm": syn.REDDIT_LIKE, "c4_attention": syn.ARXIV_LIKE,
+            "c5_spmm": syn.PRODUCTS_LIKE}[name]
+    crow, col, info = syn.powerlaw_csr(spec, seed=0, device=device)
+    n = info["rows"]
+    w = {"name": name, "spec": spec, "info": info, "crow": crow, "col": col, "f": f, "n": n}
+    if name == "c2_spmm":
+        w["val"] = syn.edge_values(info["nnz"], seed=0, device=device)
+        w["x"] = syn.dense(n, f, 3, device)
+    elif name == "c5_spmm":
+        w["val"] = None
+        w["x"] = syn.dense(n, f, 3, device)
+    elif name == "c3_sddmm":
+        w["q"], w["k"] = syn.dense(n, f, 1, device), syn.dense(n, f, 2, device)
+    else:
+        w["q"], w["k"], w["v"] = syn.dense(n, f, 1, device), syn.dense(n, f, 2, device), syn.dense(n, f, 3, device)
+    return w
+
+
+def run_ours_single(args) -> dict:
+    import autosage_b200
+    from autosage_b200 import _native
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device")
+    if not autosage_b200.load_native():
+        raise RuntimeError(f"libautosage_b200.so failed to load: {autosage_b200.ops.native_load_error()}")
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    w = build_workload(args.workload, args.features, device)
+    n, nnz, f = w["n"], w["info"]["nnz"], w["f"]
+    crow, col = w["crow"], w["col"]
+    tile, warps, threshold = args.tile, args.warps, args.hub_threshold
+    stream = torch.cuda.current_stream()
+
+    if args.workload in ("c2_spmm", "c5_spmm"):
+        val, x = w["val"], w["x"]
+        y = torch.empty(n, f, device=device)
+        ws, _ = _native.planned_workspace(crow, threshold)
+        _native.plan_build(crow, threshold, ws)
+
+        def step():
+            _native.spmm(crow, col, val, x, y, feature_tile=tile, warps=warps, threshold=threshold,
+                         flags=_native.FLAG_PLAN_READY, workspace=ws)
+
+        algorithmic = spmm_bytes(n, nnz, f, val is not None)
+        kernel_name = "spmm_kernel"
+        host_inputs = [crow, col, x] + ([val] if val is not None else [])
+
+        def e2e_step(dev_inputs):
+            c, cc, xx = dev_inputs[0], dev_inputs[1], dev_inputs[2]
+            vv = dev_inputs[3] if len(dev_inputs) > 3 else None
+            return torch.ops.autosage.spmm_csr_split(c, cc, vv, xx, tile if tile in (64, 128) else 128,
+                                                     warps if warps in (2, 4, 8) else 8, threshold)
+    elif args.workload == "c3_sddmm":
+        q, k = w["q"], w["k"]
+        out = torch.empty(nnz, device=device)
+        ws, _ = _native.planned_workspace(crow, threshold)
+        _native.plan_build(crow, threshold, ws)
+
+        def step():
+            _native.sddmm(crow, col, q, k, out, warps=warps, threshold=threshold, flags=_native.FLAG_PLAN_READY,
+                          workspace=ws)
+
+        algorithmic = sddmm_bytes(n, nnz, f)
+        kernel_name = "sddmm_kernel"
+        host_inputs = [crow, col, q, k]
+
+        def e2e_step(dev_inputs):
+            return torch.ops.autosage.sddmm_csr_split(*dev_inputs, warps if warps in (2, 4, 8) else 8, threshold)
+    else:
+        q, k, v = w["q"], w["k"], w["v"]
+        out = torch.empty(n, f, device=device)
+        ws, _ = _native.planned_workspace(crow, threshold)
+        _native.plan_build(crow, threshold, ws)
+        scale = f ** -0.5
+
+        def step():
+            _native.attention(crow, col, q, k, v, out, scale=scale, warps=warps, threshold=threshold,
+                              flags=_native.FLAG_PLAN_READY, workspace=ws)
+
+        algorithmic = attention_bytes(n, nnz, f)
+        kernel_name = "attention_kernel"
+        host_inputs = [crow, col, q, k, v]
+
+        def e2e_step(dev_inputs):
+            c, cc, qq, kk, vv = dev_inputs
+            o = torch.empty_like(vv)
+            w2, ready = _native.planned_workspace(c, threshold)
+            _native.attention(c, cc, qq, kk, vv, o, scale=scale, warps=warps, threshold=threshold, flags=ready,
+                              workspace=w2)
+            return o
+
+    # ---- device-resident timing -------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler(0) as clocks:
+        torch.cuda.synchronize()
+        t_begin = torch.cuda.Event(enable_timing=True)
+        t_end = torch.cuda.Event(enable_timing=True)
+        t_begin.record(stream)
+        for i in range(args.steps):
+            starts[i].record(stream)
+            step()
+            stops[i].record(stream)
+        t_end.record(stream)
+        torch.cuda.synchronize()
+    total_ms = t_begin.elapsed_time(t_end)
+    per_launch = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+    ms_per_step = total_ms / args.steps
+    status = _native.workspace_status(ws)
+    if status != 0:
+        raise RuntimeError(f"a kernel reported status {status}; the timing is invalid")
+    value = algorithmic / (ms_per_step * 1e-3) / 1e9
+    launch_ms = statistics.fmean(per_launch)
+    peak, peak_kind = measured_peak()
+    achieved = algorithmic / (launch_ms * 1e-3) / 1e9
+
+    # ---- end to end through the public operators, host buffers ----------------------------------
+    pinned = [t.cpu().pin_memory() for t in host_inputs]
+    h2d_bytes = sum(t.numel() * t.element_size() for t in pinned)
+    result_host = None
+    e2e_steps = max(2, min(args.steps, 5))
+
+    def e2e_once():
+        nonlocal result_host
+        dev_inputs = [t.to(device, non_blocking=True) for t in pinned]
+        res = e2e_step(dev_inputs)
+        if result_host is None:
+            result_host = torch.empty(res.shape, dtype=res.dtype).pin_memory()
+        result_host.copy_(res, non_blocking=True)
+
+    del host_inputs
+    e2e_once()
+    torch.cuda.synchronize()
+    e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_begin.record(stream)
+    for _ in range(e2e_steps):
+        e2e_once()
+    e_end.record(stream)
+    torch.cuda.synchronize()
+    e2e_ms = e_begin.elapsed_time(e_end) / e2e_steps
+    d2h_bytes = result_host.numel() * result_host.element_size()
+
+    line = {
+        "metric": "algorithmic_GBps",
+        "value": round(value, 2),
+        "unit": "GB/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "f32",
+        "data": "synthetic",
+        "config": {
+            "workload": f"{args.workload}: power-law CSR {n} rows, {nnz} nnz, F={f}"
+                        + (", weighted" if args.workload == "c2_spmm" else ""),
+            "kernel_parameters": {"feature_tile": tile, "warps_per_block": warps, "hub_threshold": threshold},
+            "l2": "inputs per step (CSR + dense operand, %.2f GB) exceed the 126 MB L2; no explicit flush"
+                  % ((8 * nnz + 4 * nnz + 4 * n * f) / 1e9),
+            "plan": "degree-binned plan cached (replay path)",
+        },
+        "edges_f_per_s": round(nnz * f / (ms_per_step * 1e-3), 1),
+        "algorithmic_bytes_per_step": algorithmic,
+        "pct_of_8TBps": round(100.0 * value / 8000.0, 2),
+        "roofline": {
+            "bound": "hbm",
+            "kernel": kernel_name,
+            "achieved": round(achieved, 2),
+            "peak": peak,
+            "peak_source": f"{peak_kind} HBM copy bandwidth (burst)",
+            "unit": "GB/s",
+            "frac": round(achieved / peak, 4),
+            "traffic": None,
+            "launch_ms": round(launch_ms, 4),
+        },
+        "e2e": {
+            "value": round(algorithmic / (e2e_ms * 1e-3) / 1e9, 2),
+            "unit": "GB/s",
+            "ms_per_step": round(e2e_ms, 3),
+            "h2d_bytes_per_step": h2d_bytes,
+            "d2h_bytes_per_step": d2h_bytes,
+            "steps": e2e_steps,
+        },
+        "gpu_launches": args.steps,
+        "clocks": clocks.summary(),
+    }
+
+    if not args.no_cpu_baseline and args.workload in ("c2_spmm", "c5_spmm"):
+        from oracle import oracle
+
+        crow_c, col_c = crow.cpu(), col.cpu()
+        val_c = None if w.get("val") is None else w["val"].cpu()
+        x_c = w["x"].cpu()
+        seconds, rows, sample_nnz = cpu_spmm_sample(crow_c, col_c, val_c, x_c, args.cpu_sample_nnz, 2)
+        sample_bytes = spmm_bytes(rows, sample_nnz, f, val_c is not None)
+        line["cpu_baseline"] = {
+            "value": round(sample_bytes / seconds / 1e9, 3),
+            "unit": "GB/s",
+            "cores": torch.get_num_threads(),
+            "host_cpus": os.cpu_count(),
+            "kind": "port",
+            "sample": f"first {rows} rows ({sample_nnz} nnz) of the same CSR against the full X, "
+                      f"torch.sparse.mm on CPU float32 (the reference's CPU path), best of 2 after 1 warm-up, "
+                      f"{seconds:.3f} s per call",
+            "edges_f_per_s": round(sample_nnz * f / seconds, 1),
+            "oracle_threads": oracle.threads(),
+        }
+    return line
+
+
+def run_reference(args) -> dict:
+    """The reference's CPU implementation of the path (torch.sparse.mm over a CSR tensor, as
+    restated in oracle/) on this host's cores; each step is one call on a bounded row sample."""
+    from autosage_b200 import synthetic as syn
+
+    spec = syn.REDDIT_LIKE if args.workload != "c5_spmm" else syn.PRODUCTS_LIKE
+    # Only the sampled rows are materialised on the host: same degree sequence as the GPU arm's
+    # graph, columns iid uniform over all N columns and sorted inside each row.
+    degree, _ = syn.powerlaw_degrees(spec.rows, spec.target_nnz, spec.alpha, spec.max_degree, 0)
+    n, f = spec.rows, args.features
+    info = {"rows": n, "nnz": int(degree.sum())}
+    weighted = args.workload != "c5_spmm"
+    from oracle import oracle
+
+    crow = torch.zeros(n + 1, dtype=torch.long)
+    torch.cumsum(degree, 0, out=crow[1:])
+    rows = int(torch.searchsorted(crow, torch.tensor(args.cpu_sample_nnz)).clamp(1, n))
+    sub_crow, sub_col = syn.csr_from_degrees(degree[:rows], n, seed=0)
+    nnz = int(sub_crow[-1])
+    sub_val = syn.edge_values(nnz, seed=0) if weighted else None
+    x = syn.dense(n, f, 3)
+    for _ in range(max(1, min(args.warmup, 2))):
+        oracle.spmm_reference_cpu(sub_crow, sub_col, sub_val, x)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.spmm_reference_cpu(sub_crow, sub_col, sub_val, x)
+    seconds = (time.perf_counter() - t0) / args.steps
+    sample_bytes = spmm_bytes(rows, nnz, f, weighted)
+    value = round(sample_bytes / seconds / 1e9, 3)
+    sample = (f"first {rows} rows ({nnz} nnz) of the {info['rows']}-row CSR against the full X; "
+              f"torch.sparse.mm on CPU float32")
+    return {
+        "impl": "reference",
+        "metric": "algorithmic_GBps",
+        "value": value,
+        "unit": "GB/s",
+        "n_gpus": args.gpus,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(seconds * 1e3, 3),
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: power-law CSR {n} rows, {info['nnz']} nnz, F={f}"
+                               + (", weighted" if weighted else ""), "sample": sample},
+        "edges_f_per_s": round(nnz * f / seconds, 1),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--workload", default=None)
+    parser.add_argument("--features", type=int, default=128)
+    parser.add_argument("--tile", type=int, default=128)
+    parser.add_argument("--warps", type=int, default=8)
+    parser.add_argument("--hub-threshold", type=int, default=1566)
+    parser.add_argument("--cpu-sample-nnz", type=int, default=4_000_000)
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if args.workload is None:
+        args.workload = "c2_spmm" if max(args.gpus, world) == 1 else "c5_spmm"
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference(args)), flush=True)
+        return
+    if world > 1 or args.gpus > 1:
+        from autosage_b200 import dist_bench
+
+        line = dist_bench.run(args)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return
+    print(json.dumps(run_ours_single(args)), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,154 @@
+/*
+ * autosage_b200.h — C ABI of libautosage_b200.so (CUDA, sm_100a).
+ *
+ * The library is the device side of AutoSAGE's sparse hot path: CSR SpMM, CSR SDDMM, CSR row
+ * softmax and the fused SDDMM -> softmax -> SpMM attention row kernel.  Every entry point takes
+ * plain device pointers and sizes, launches on the stream it is given, never synchronises the
+ * device, never allocates device memory and never throws.  Return value: 0 on success, a negative
+ * ASG_E* code otherwise; asg_last_error_string() gives the message for the calling thread.
+ *
+ * Conventions shared by all entry points
+ *   crow   int64[n_rows+1]  CSR row pointers (device), crow[0] may be non-zero only if col/val are
+ *                           indexed by the same absolute positions
+ *   col    int64[nnz]       column indices (device); every value must be < 2^31
+ *   val    float32[nnz]     edge weights (device) or NULL for an all-ones matrix
+ *   x,q,k,v float32 row-major dense operands with leading dimension f (device)
+ *   stream a cudaStream_t passed as void* (NULL = the legacy default stream)
+ *   workspace  caller-owned device scratch of at least asg_workspace_bytes(n_rows) bytes, 256-byte
+ *              aligned; it holds the degree-binned row order ("plan") and the work counters of the
+ *              persistent kernels.  One workspace serves one stream at a time.
+ *
+ * Reference interfaces replaced (paths inside the AutoSAGE repository):
+ *   asg_spmm_csr          csrc/spmm_csr_vec4.cu:97-176   spmm_csr_cuda  (op autosage::spmm_csr,
+ *                         csrc/spmm_binding.cpp:31-38)
+ *   asg_spmm_csr_split    csrc/launcher_spmm.cu:22-72    spmm_csr_split_cuda (op
+ *                         autosage::spmm_csr_split, csrc/spmm_binding.cpp:40-61), including the
+ *                         row launchers csrc/spmm_rows.cu:132-157 and csrc/spmm_hub.cu:149-182
+ *   asg_plan_build        csrc/launcher_spmm.cu:49-59    the per-call hub/light row split
+ *   asg_sddmm_csr         csrc/sddmm_csr_op.cu:108-134   sddmm_csr
+ *   asg_sddmm_csr_split   csrc/sddmm_csr_op.cu:136-187   sddmm_csr_split
+ *   asg_csr_row_softmax   autosage/_auto.py:744-759      _csr_row_softmax
+ *   asg_csr_attention     autosage/_auto.py:762-780      csr_attention_forward's three passes,
+ *                         fused into one kernel
+ */
+#ifndef AUTOSAGE_B200_H_
+#define AUTOSAGE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ASG_OK 0
+#define ASG_EINVAL (-1)    /* bad argument (message says which) */
+#define ASG_ECUDA (-2)     /* a CUDA runtime call or kernel launch failed */
+#define ASG_EWORKSPACE (-3) /* workspace missing, misaligned or too small */
+#define ASG_ERANGE (-4)    /* a size exceeds what the kernels index (2^31-1 rows / features) */
+
+/* flags for the *_ex entry points */
+#define ASG_FLAG_ACCUMULATE 1u /* y += A x instead of y = A x */
+#define ASG_FLAG_NO_VEC4 2u    /* force the scalar kernels (AUTOSAGE_VEC4=0 in the reference) */
+#define ASG_FLAG_PLAN_READY 4u /* workspace already holds a plan for this crow/threshold */
+#define ASG_FLAG_NO_BULK_STAGE 8u /* hub rows: stage col/val with plain loads, not bulk copies */
+
+/* Library version: major*10000 + minor*100 + patch. */
+int asg_version(void);
+
+/* Message of the last failing call made by this thread ("" if none). */
+const char* asg_last_error_string(void);
+
+/* Bytes of workspace needed for a graph with n_rows rows (0 rows -> still a small header). */
+size_t asg_workspace_bytes(int64_t n_rows);
+
+/*
+ * Degree-bin the rows of a CSR matrix into the workspace: rows with degree >= hub_threshold
+ * ("hubs", processed one CTA each) come first, then the light rows (one warp each); inside each
+ * class rows are ordered by descending floor(log2(degree)) and, within a bucket, by ascending row
+ * id, so the result is deterministic.  hub_threshold <= 0 disables the hub class.
+ * Replaces the nonzero()/cast sequence the reference runs on every call
+ * (csrc/launcher_spmm.cu:49-59, csrc/sddmm_csr_op.cu:169-171) with three small kernels and no
+ * host synchronisation.
+ */
+int asg_plan_build(const int64_t* crow, int64_t n_rows, int64_t hub_threshold, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/*
+ * Copy the plan out for inspection: order[n_rows] (int32 row ids in processing order) and
+ * counts[2] = {n_hub, n_light}.  Both are device pointers; either may be NULL.
+ */
+int asg_plan_export(const void* workspace, int64_t n_rows, int32_t* order, int32_t* counts,
+                    void* stream);
+
+/*
+ * y[n_rows, f] = A x.  Plain SpMM (reference op autosage::spmm_csr).  Chooses the feature tile and
+ * hub threshold itself.  x must have at least max(col)+1 rows of f floats.
+ */
+int asg_spmm_csr(const int64_t* crow, const int64_t* col, const float* val, const float* x,
+                 float* y, int64_t n_rows, int64_t nnz, int64_t f, void* workspace,
+                 size_t workspace_bytes, void* stream);
+
+/*
+ * SpMM with the reference's three tuning knobs (op autosage::spmm_csr_split):
+ *   feature_tile     64 or 128 (also 32 and 256 through this ABI): features handled per pass
+ *   warps_per_block  2, 4, 8 (also 16): warps of each CTA; a hub row is shared by all of them
+ *   hub_threshold    rows with degree >= threshold take the CTA-per-hub path (> 0)
+ */
+int asg_spmm_csr_split(const int64_t* crow, const int64_t* col, const float* val, const float* x,
+                       float* y, int64_t n_rows, int64_t nnz, int64_t f, int feature_tile,
+                       int warps_per_block, int64_t hub_threshold, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* As asg_spmm_csr_split, plus ASG_FLAG_* bits. */
+int asg_spmm_csr_ex(const int64_t* crow, const int64_t* col, const float* val, const float* x,
+                    float* y, int64_t n_rows, int64_t nnz, int64_t f, int feature_tile,
+                    int warps_per_block, int64_t hub_threshold, unsigned flags, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/* out[nnz]: out[e] = <q[row(e), :], k[col[e], :]>  (reference op autosage::sddmm_csr). */
+int asg_sddmm_csr(const int64_t* crow, const int64_t* col, const float* q, const float* k,
+                  float* out, int64_t n_rows, int64_t nnz, int64_t f, void* workspace,
+                  size_t workspace_bytes, void* stream);
+
+/* SDDMM with the reference's two knobs (op autosage::sddmm_csr_split). */
+int asg_sddmm_csr_split(const int64_t* crow, const int64_t* col, const float* q, const float* k,
+                        float* out, int64_t n_rows, int64_t nnz, int64_t f, int warps_per_block,
+                        int64_t hub_threshold, void* workspace, size_t workspace_bytes,
+                        void* stream);
+
+/* As asg_sddmm_csr_split, plus ASG_FLAG_* bits (ACCUMULATE is not accepted). */
+int asg_sddmm_csr_ex(const int64_t* crow, const int64_t* col, const float* q, const float* k,
+                     float* out, int64_t n_rows, int64_t nnz, int64_t f, int warps_per_block,
+                     int64_t hub_threshold, unsigned flags, void* workspace,
+                     size_t workspace_bytes, void* stream);
+
+/*
+ * probs[nnz] = softmax over each CSR row segment of scores[nnz]
+ * (exp(s - rowmax) / sum exp(s - rowmax)); empty rows write nothing.  scores and probs may alias.
+ */
+int asg_csr_row_softmax(const int64_t* crow, const float* scores, float* probs, int64_t n_rows,
+                        int64_t nnz, int warps_per_block, int64_t hub_threshold, unsigned flags,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * out[n_rows, f] = softmax_row(scale * (q k^T restricted to the CSR pattern)) v, computed in one
+ * pass with a running maximum and running sum per row, so scores and probabilities never reach
+ * memory.  Rows without edges produce zeros.  scale = 1.0 reproduces the reference pipeline.
+ */
+int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, const float* k,
+                      const float* v, float* out, int64_t n_rows, int64_t nnz, int64_t f,
+                      float scale, int warps_per_block, int64_t hub_threshold, unsigned flags,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Status word written by kernels whose bounded waits gave up (0 = none).  The word lives in the
+ * workspace header; this reads it back asynchronously into *host_status (pinned or pageable host
+ * memory) on the given stream.  Non-zero means the output of the launch that set it is invalid.
+ */
+int asg_workspace_status(const void* workspace, int32_t* host_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AUTOSAGE_B200_H_ */

@@ -1,0 +1,373 @@
+"""GPU parity: the sm_100a kernels, called through the C ABI, against the CPU oracle.
+
+Tolerance for float32 results, from the project's acceptance rule: against the float64 oracle,
+|y - y64| <= 1e-5*|y64| + 1e-5*sqrt(row degree); integer outputs must be bit-exact.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import csr_from_counts, dense, misaligned_copy, random_csr, to_np, weights
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-5
+ATOL = 1e-5  # multiplied by sqrt(row degree)
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import autosage_b200
+    from autosage_b200 import _native
+
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    assert autosage_b200.load_native(), f"native library failed to load: {autosage_b200.ops.native_load_error()}"
+    return _native
+
+
+@pytest.fixture(scope="module")
+def orc():
+    from oracle import oracle
+
+    return oracle
+
+
+def assert_close(orc, actual: torch.Tensor, exact: np.ndarray, crow, per_edge=False):
+    ok, ratio = orc.within_tolerance(actual.detach().cpu().numpy(), exact, to_np(crow), per_edge=per_edge,
+                                     rtol=RTOL, atol=ATOL)
+    assert ok, f"outside rtol {RTOL} / atol {ATOL}*sqrt(deg): worst error/bound = {ratio:.3f}"
+
+
+def run_spmm(lib, crow, col, val, x, *, tile=128, warps=8, threshold=64, flags=0, y=None, ws=None):
+    dev = torch.device("cuda")
+    crow_d, col_d, x_d = crow.to(dev), col.to(dev), x if x.is_cuda else x.to(dev)
+    val_d = None if val is None else val.to(dev)
+    n = crow.numel() - 1
+    if y is None:
+        y = torch.full((n, x.size(1)), float("nan"), device=dev)
+    if ws is None:
+        ws = torch.empty(lib.workspace_bytes(n), dtype=torch.uint8, device=dev)
+    lib.spmm(crow_d, col_d, val_d, x_d, y, feature_tile=tile, warps=warps, threshold=threshold, flags=flags,
+             workspace=ws)
+    torch.cuda.synchronize()
+    assert lib.workspace_status(ws) == 0
+    return y
+
+
+# ------------------------------------------------------------------------------------------ plan
+@pytest.mark.parametrize("rows,threshold", [(1, 1), (31, 4), (1024, 9), (1025, 9), (5000, 1), (5000, 0), (70000, 33)])
+def test_plan_order_is_bit_exact(lib, orc, rows, threshold):
+    crow, _ = random_csr(rows, 8, seed=rows, hubs={0: 700, rows // 2: 40})
+    ws = torch.empty(lib.workspace_bytes(rows), dtype=torch.uint8, device="cuda")
+    lib.plan_build(crow.cuda(), threshold, ws)
+    order, counts = lib.plan_export(ws, rows)
+    expected, n_hub, n_light = orc.plan_order(to_np(crow), threshold)
+    assert counts.cpu().tolist() == [n_hub, n_light]
+    assert np.array_equal(order.cpu().numpy(), expected)
+    # the hub set is the reference's nonzero(deg >= T), which is ascending
+    hubs, lights = orc.hub_split(to_np(crow), threshold)
+    assert np.array_equal(np.sort(order.cpu().numpy()[:n_hub]), hubs)
+    assert np.array_equal(np.sort(order.cpu().numpy()[n_hub:]), lights)
+
+
+# ------------------------------------------------------------------------------------------ SpMM
+@pytest.mark.parametrize("features", [1, 3, 4, 32, 64, 100, 113, 128, 192, 256, 512])
+@pytest.mark.parametrize("weighted", [False, True])
+def test_spmm_feature_widths(lib, orc, features, weighted):
+    crow, col = random_csr(300, 12, seed=features, hubs={7: 900, 150: 64})
+    x = dense(300, features, seed=1)
+    val = weights(col.numel(), 2) if weighted else None
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    for tile in (64, 128):
+        y = run_spmm(lib, crow, col, val, x, tile=tile, warps=8, threshold=64)
+        assert_close(orc, y, exact, crow)
+
+
+@pytest.mark.parametrize("tile", [32, 64, 128, 256])
+@pytest.mark.parametrize("warps", [2, 4, 8, 16])
+def test_spmm_tile_and_warp_grid(lib, orc, tile, warps):
+    crow, col = random_csr(257, 20, seed=tile + warps, hubs={0: 3000, 100: 1500, 256: 700})
+    x = dense(257, 200, seed=3)
+    val = weights(col.numel(), 4)
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    y = run_spmm(lib, crow, col, val, x, tile=tile, warps=warps, threshold=500)
+    assert_close(orc, y, exact, crow)
+
+
+@pytest.mark.parametrize("flags_name", ["default", "no_vec4", "no_bulk", "no_vec4_no_bulk"])
+def test_spmm_code_paths(lib, orc, flags_name):
+    flags = {"default": 0, "no_vec4": lib.FLAG_NO_VEC4, "no_bulk": lib.FLAG_NO_BULK_STAGE,
+             "no_vec4_no_bulk": lib.FLAG_NO_VEC4 | lib.FLAG_NO_BULK_STAGE}[flags_name]
+    crow, col = random_csr(400, 10, seed=9, hubs={3: 5000, 399: 2049})
+    x = dense(400, 128, seed=5)
+    val = weights(col.numel(), 6)
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    y = run_spmm(lib, crow, col, val, x, threshold=100, flags=flags)
+    assert_close(orc, y, exact, crow)
+    y = run_spmm(lib, crow, col, None, x, threshold=100, flags=flags)
+    assert_close(orc, y, orc.spmm(to_np(crow), to_np(col), None, to_np(x)), crow)
+
+
+def test_spmm_degrees_at_bin_and_chunk_edges(lib, orc):
+    # 32-edge batches, the 4-edge staging alignment, and the 128*warps staging chunk
+    degrees = [0, 1, 2, 3, 4, 5, 7, 8, 9, 31, 32, 33, 63, 64, 65, 127, 128, 129, 255, 256, 257, 511, 512, 513,
+               1023, 1024, 1025, 1026, 1027, 2047, 2048, 2049, 4095, 4096, 4097, 0, 0, 6]
+    crow, col = csr_from_counts(degrees, len(degrees), seed=77)
+    x = dense(len(degrees), 96, seed=8)
+    val = weights(col.numel(), 9)
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    for threshold in (1, 32, 33, 1024, 100000):
+        for warps in (2, 8):
+            y = run_spmm(lib, crow, col, val, x, tile=64, warps=warps, threshold=threshold)
+            assert_close(orc, y, exact, crow)
+
+
+def test_spmm_empty_shapes(lib, orc):
+    # all rows empty
+    crow = torch.zeros(50, dtype=torch.long)
+    col = torch.zeros(0, dtype=torch.long)
+    x = dense(49, 64, seed=1)
+    y = run_spmm(lib, crow, col, None, x)
+    assert torch.equal(y.cpu(), torch.zeros(49, 64))
+    # zero rows / zero features: nothing to launch, status OK
+    lib.check(lib.library().asg_spmm_csr_ex(None, None, None, None, None, 0, 0, 64, 64, 8, 16, 0, None, 0, None))
+    lib.check(lib.library().asg_spmm_csr_ex(None, None, None, None, None, 10, 0, 0, 64, 8, 16, 0, None, 0, None))
+
+
+def test_spmm_misaligned_operands_take_scalar_path(lib, orc):
+    crow, col = random_csr(200, 9, seed=31, hubs={5: 1200})
+    x = dense(200, 128, seed=2)
+    val = weights(col.numel(), 3)
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    x_off = misaligned_copy(x.cuda())          # 4-byte offset: neither 16- nor 32-byte aligned
+    assert x_off.data_ptr() % 16 != 0
+    y = run_spmm(lib, crow, col, val, x_off, threshold=100)
+    assert_close(orc, y, exact, crow)
+    x16 = misaligned_copy(x.cuda(), 4)         # 16-byte aligned only: 128-bit loads
+    assert x16.data_ptr() % 32 != 0 and x16.data_ptr() % 16 == 0
+    y = run_spmm(lib, crow, col, val, x16, threshold=100)
+    assert_close(orc, y, exact, crow)
+    # misaligned col/val force the plain-load staging of hub rows
+    col_off = misaligned_copy(col.cuda())
+    val_off = misaligned_copy(val.cuda())
+    assert col_off.data_ptr() % 16 != 0
+    y = run_spmm(lib, crow, col_off, val_off, x, threshold=100)
+    assert_close(orc, y, exact, crow)
+
+
+def test_spmm_accumulate_and_plan_reuse(lib, orc):
+    crow, col = random_csr(500, 14, seed=41, hubs={10: 2500})
+    x = dense(500, 160, seed=4)
+    val = weights(col.numel(), 5)
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    ws = torch.empty(lib.workspace_bytes(500), dtype=torch.uint8, device="cuda")
+    y = run_spmm(lib, crow, col, val, x, threshold=200, ws=ws)
+    assert_close(orc, y, exact, crow)
+    # same workspace, plan kept: three more launches, the last two accumulating
+    y2 = run_spmm(lib, crow, col, val, x, threshold=200, ws=ws, flags=lib.FLAG_PLAN_READY)
+    assert torch.equal(y, y2)
+    y3 = run_spmm(lib, crow, col, val, x, threshold=200, ws=ws, flags=lib.FLAG_PLAN_READY | lib.FLAG_ACCUMULATE, y=y2)
+    assert_close(orc, y3, 2 * exact, crow)
+
+
+def test_spmm_rectangular_column_space(lib, orc):
+    """Rows of a shard index a taller X (the multi-GPU layout): 64 rows, 1000 columns."""
+    counts = torch.randint(0, 40, (64,), generator=torch.Generator().manual_seed(2))
+    counts[3] = 700
+    crow, col = csr_from_counts(counts, 1000, seed=5)
+    x = dense(1000, 128, seed=6)
+    val = weights(col.numel(), 7)
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    y = run_spmm(lib, crow, col, val, x, threshold=128)
+    assert_close(orc, y, exact, crow)
+
+
+def test_spmm_entry_points_agree(lib, orc):
+    crow, col = random_csr(350, 11, seed=51, hubs={1: 2600})
+    x = dense(350, 128, seed=7).cuda()
+    val = weights(col.numel(), 8).cuda()
+    crow_d, col_d = crow.cuda(), col.cuda()
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    ws = torch.empty(lib.workspace_bytes(350), dtype=torch.uint8, device="cuda")
+    y_plain = torch.empty_like(x)
+    lib.spmm_plain(crow_d, col_d, val, x, y_plain, ws)
+    y_split = torch.empty_like(x)
+    lib.spmm_split_strict(crow_d, col_d, val, x, y_split, 64, 4, 300, ws)
+    torch.cuda.synchronize()
+    assert_close(orc, y_plain, exact, crow)
+    assert_close(orc, y_split, exact, crow)
+    with pytest.raises(RuntimeError, match="hub_threshold must be positive"):
+        lib.spmm_split_strict(crow_d, col_d, val, x, y_split, 64, 4, 0, ws)
+    with pytest.raises(RuntimeError, match="workspace"):
+        lib.spmm_plain(crow_d, col_d, val, x, y_plain, ws[:128])
+
+
+# ----------------------------------------------------------------------------------------- SDDMM
+def run_sddmm(lib, crow, col, q, k, *, warps=8, threshold=64, flags=0):
+    dev = torch.device("cuda")
+    out = torch.full((col.numel(),), float("nan"), device=dev)
+    ws = torch.empty(lib.workspace_bytes(crow.numel() - 1), dtype=torch.uint8, device=dev)
+    q_d = q if q.is_cuda else q.to(dev)
+    k_d = k if k.is_cuda else k.to(dev)
+    lib.sddmm(crow.to(dev), col.to(dev), q_d, k_d, out, warps=warps, threshold=threshold, flags=flags, workspace=ws)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("features", [1, 3, 4, 32, 64, 100, 113, 128, 192, 256, 512, 640, 1024])
+def test_sddmm_feature_widths(lib, orc, features):
+    crow, col = random_csr(260, 10, seed=features + 1, hubs={9: 1100, 200: 65})
+    q, k = dense(260, features, 11), dense(260, features, 12)
+    exact = orc.sddmm(to_np(crow), to_np(col), to_np(q), to_np(k))
+    for warps, threshold in ((8, 64), (2, 1), (4, 100000)):
+        out = run_sddmm(lib, crow, col, q, k, warps=warps, threshold=threshold)
+        ok, ratio = orc.within_tolerance(out.cpu().numpy(), exact, to_np(crow), per_edge=True, rtol=RTOL, atol=ATOL)
+        assert ok, f"worst error/bound {ratio:.3f}"
+
+
+def test_sddmm_scalar_and_misaligned_paths(lib, orc):
+    crow, col = random_csr(180, 8, seed=61, hubs={4: 800})
+    q, k = dense(180, 128, 13), dense(180, 128, 14)
+    exact = orc.sddmm(to_np(crow), to_np(col), to_np(q), to_np(k))
+    for out in (run_sddmm(lib, crow, col, q, k, flags=lib.FLAG_NO_VEC4),
+                run_sddmm(lib, crow, col, misaligned_copy(q.cuda()), k),
+                run_sddmm(lib, crow, col, q, misaligned_copy(k.cuda(), 4))):
+        ok, ratio = orc.within_tolerance(out.cpu().numpy(), exact, to_np(crow), per_edge=True, rtol=RTOL, atol=ATOL)
+        assert ok, f"worst error/bound {ratio:.3f}"
+
+
+def test_sddmm_batch_edges(lib, orc):
+    degrees = [0, 1, 31, 32, 33, 63, 64, 65, 255, 256, 257, 0, 1023, 1024, 1025, 2]
+    crow, col = csr_from_counts(degrees, len(degrees), seed=3)
+    q, k = dense(len(degrees), 64, 15), dense(len(degrees), 64, 16)
+    exact = orc.sddmm(to_np(crow), to_np(col), to_np(q), to_np(k))
+    for warps, threshold in ((2, 32), (8, 33), (16, 1), (4, 5000)):
+        out = run_sddmm(lib, crow, col, q, k, warps=warps, threshold=threshold)
+        ok, ratio = orc.within_tolerance(out.cpu().numpy(), exact, to_np(crow), per_edge=True, rtol=RTOL, atol=ATOL)
+        assert ok, f"worst error/bound {ratio:.3f}"
+
+
+# --------------------------------------------------------------------------- softmax & attention
+def test_row_softmax_matches_oracle(lib, orc):
+    degrees = [0, 1, 2, 31, 32, 33, 700, 5, 0, 3000, 64]
+    crow, _ = csr_from_counts(degrees, 11, seed=1)
+    scores = 11.0 * dense(int(crow[-1]), 1, 17).flatten()   # peaked rows, like unscaled F=128 scores
+    exact = orc.row_softmax(to_np(crow), to_np(scores).astype(np.float64))
+    for warps, threshold in ((8, 512), (2, 1), (4, 100000)):
+        probs = torch.empty_like(scores, device="cuda")
+        ws = torch.empty(lib.workspace_bytes(11), dtype=torch.uint8, device="cuda")
+        lib.row_softmax(crow.cuda(), scores.cuda(), probs, warps=warps, threshold=threshold, flags=0, workspace=ws)
+        torch.cuda.synchronize()
+        np.testing.assert_allclose(probs.cpu().numpy(), exact, rtol=2e-5, atol=1e-7)
+        sums = torch.segment_reduce(probs.cpu(), "sum", lengths=torch.tensor(degrees))
+        nonempty = torch.tensor(degrees) > 0
+        assert torch.allclose(sums[nonempty], torch.ones(int(nonempty.sum())), atol=1e-5)
+
+
+@pytest.mark.parametrize("features", [4, 32, 64, 100, 128, 256, 512])
+@pytest.mark.parametrize("scale", [1.0, None])
+def test_fused_attention_matches_three_pass_oracle(lib, orc, features, scale):
+    crow, col = random_csr(220, 9, seed=features, hubs={2: 1500, 100: 66})
+    q, k, v = dense(220, features, 21), dense(220, features, 22), dense(220, features, 23)
+    s = float(features) ** -0.5 if scale is None else scale
+    exact = orc.attention(to_np(crow), to_np(col), to_np(q), to_np(k), to_np(v), s)
+    for warps, threshold in ((8, 64), (2, 1), (4, 100000)):
+        out = torch.full((220, features), float("nan"), device="cuda")
+        ws = torch.empty(lib.workspace_bytes(220), dtype=torch.uint8, device="cuda")
+        lib.attention(crow.cuda(), col.cuda(), q.cuda(), k.cuda(), v.cuda(), out, scale=s, warps=warps,
+                      threshold=threshold, flags=0, workspace=ws)
+        torch.cuda.synchronize()
+        assert_close(orc, out, exact, crow)
+
+
+def test_fused_attention_rejects_wide_rows(lib):
+    crow, col = random_csr(8, 2, seed=1)
+    t = torch.zeros(8, 516, device="cuda")
+    ws = torch.empty(lib.workspace_bytes(8), dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="512 features"):
+        lib.attention(crow.cuda(), col.cuda(), t, t, t, torch.empty_like(t), scale=1.0, warps=8, threshold=64,
+                      flags=0, workspace=ws)
+
+
+# ----------------------------------------------------------------------------- golden fixtures
+@pytest.mark.parametrize("case", ["tiny", "ragged", "hub", "wide"])
+def test_kernels_match_reference_outputs(lib, orc, golden, case):
+    """Outputs of the reference itself (float64 CPU run) are the expected values here."""
+    vec, _ = golden
+    crow, col = torch.from_numpy(vec[f"{case}.crow"]), torch.from_numpy(vec[f"{case}.col"])
+    x, q, k = (torch.from_numpy(vec[f"{case}.{n}"]) for n in ("x", "q", "k"))
+    val = torch.from_numpy(vec[f"{case}.val"])
+    y = run_spmm(lib, crow, col, val, x, threshold=32)
+    assert_close(orc, y, vec[f"{case}.spmm_weighted"], crow)
+    y = run_spmm(lib, crow, col, None, x, threshold=32)
+    assert_close(orc, y, vec[f"{case}.spmm_unweighted"], crow)
+    out = run_sddmm(lib, crow, col, q, k, threshold=32)
+    ok, ratio = orc.within_tolerance(out.cpu().numpy(), vec[f"{case}.sddmm"], to_np(crow), per_edge=True)
+    assert ok, ratio
+    att = torch.empty(x.shape, device="cuda")
+    ws = torch.empty(lib.workspace_bytes(crow.numel() - 1), dtype=torch.uint8, device="cuda")
+    lib.attention(crow.cuda(), col.cuda(), q.cuda(), k.cuda(), x.cuda(), att, scale=1.0, warps=8, threshold=32,
+                  flags=0, workspace=ws)
+    torch.cuda.synchronize()
+    assert_close(orc, att, vec[f"{case}.attention"], crow)
+
+
+# ------------------------------------------------------------------------- size-independent checks
+def test_full_size_spmm_properties():
+    """BASELINE configuration 2 at full size (232,965 rows, ~114.6 M nnz): properties that need no
+    oracle run. With X = ones, Y[i, :] is the sum of the row's weights; SpMM is linear in X."""
+    import autosage_b200
+    from autosage_b200 import synthetic as syn
+
+    assert autosage_b200.load_native()
+    dev = torch.device("cuda")
+    crow, col, info = syn.powerlaw_csr(syn.REDDIT_LIKE, device=dev)
+    assert abs(info["nnz"] - syn.REDDIT_LIKE.target_nnz) <= 0.005 * syn.REDDIT_LIKE.target_nnz
+    val = syn.edge_values(info["nnz"], device=dev)
+    n = info["rows"]
+    degree = crow[1:] - crow[:-1]
+    row_sum = torch.segment_reduce(val.double(), "sum", lengths=degree)
+    ones = torch.ones(n, 128, device=dev)
+    y = torch.ops.autosage.spmm_csr_split(crow, col, val, ones, 128, 8, 1566)
+    err = (y.double() - row_sum[:, None]).abs()
+    bound = 1e-5 * row_sum[:, None].abs() + 1e-5 * degree.double().sqrt()[:, None]
+    assert bool((err <= bound).all()), float((err / bound).max())
+    assert bool((y == y[:, :1]).all())  # every feature column saw the same arithmetic
+    # linearity: A(2a - b) == 2 A a - A b within rounding of the three results
+    a, b = syn.dense(n, 64, 5, dev), syn.dense(n, 64, 6, dev)
+    lhs = torch.ops.autosage.spmm_csr(crow, col, val, 2 * a - b)
+    rhs = 2 * torch.ops.autosage.spmm_csr(crow, col, val, a) - torch.ops.autosage.spmm_csr(crow, col, val, b)
+    scale = degree.double().sqrt()[:, None]
+    assert float(((lhs - rhs).abs().double() / (scale * 1e-4 + 1e-4 * rhs.abs().double())).max()) <= 1.0
+    # SDDMM: with Q = K = ones every edge scores F; softmax of equal scores is 1/degree
+    scores = torch.ops.autosage.sddmm_csr_split(crow, col, ones, ones, 8, 1566)
+    assert bool((scores == 128.0).all())
+    probs = autosage_b200._auto._csr_row_softmax(crow, scores)
+    expect = torch.repeat_interleave(1.0 / degree.double(), degree)
+    assert float((probs.double() - expect).abs().max()) <= 1e-6
+
+
+def test_full_size_attention_properties():
+    """BASELINE configuration 4 (169,343 rows, ~2.48 M nnz, F = 128): with V constant per column the
+    output of a softmax-weighted average is that constant; fused equals the three-pass pipeline."""
+    import autosage_b200
+    from autosage_b200 import synthetic as syn
+
+    dev = torch.device("cuda")
+    crow, col, info = syn.powerlaw_csr(syn.ARXIV_LIKE, device=dev)
+    n = info["rows"]
+    q, k = syn.dense(n, 128, 1, dev), syn.dense(n, 128, 2, dev)
+    v = torch.arange(128, device=dev, dtype=torch.float32).repeat(n, 1)
+    scale = 128 ** -0.5
+    fused, _ = autosage_b200.csr_attention_forward(crow, col, q, k, v, scale=scale, fused=True)
+    nonempty = (crow[1:] - crow[:-1]) > 0
+    assert torch.allclose(fused[nonempty], v[nonempty], rtol=1e-5, atol=1e-4)
+    v2 = syn.dense(n, 128, 3, dev)
+    fused, info_f = autosage_b200.csr_attention_forward(crow, col, q, k, v2, scale=scale, fused=True)
+    unfused, info_u = autosage_b200.csr_attention_forward(crow, col, q, k, v2, scale=scale, fused=False)
+    degree = (crow[1:] - crow[:-1]).double().clamp_min(1).sqrt()[:, None]
+    err = (fused.double() - unfused.double()).abs()
+    assert bool((err <= 2e-5 * unfused.abs().double() + 2e-5 * degree).all())
+    assert set(info_f) >= {"sddmm", "spmm"} and set(info_u) >= {"sddmm", "spmm"}
