@@ -1,0 +1,234 @@
+"""Row-partitioned SpMM / AutoSAGEConv over the GPUs of one node (one process per GPU).
+
+The reference is single-GPU.  For graphs that should be spread over 2/4/8 B200s the destination
+rows are cut into contiguous ranges balanced by nnz; rank r owns rows [b_r, b_{r+1}), the matching
+slice of col/val (row pointers rebased to 0), the X rows of the same range and the output rows.
+Every output row needs X rows of arbitrary columns, so X is all-gathered over NVLink: P-1 exchange
+steps on a communication stream, step s moving rank r's shard to rank (r - s) mod P while the
+shard of rank (r + s) mod P arrives.  To overlap, the local CSR is pre-split by column owner into
+P column blocks; the block of the rank's own columns is multiplied first (no wait) and each remote
+block as soon as its shard has landed, accumulating into the same output rows.  Summation order
+therefore differs from the single-GPU kernel (block by block) but stays inside the float32
+tolerance; all integer outputs (bounds, block CSRs) are deterministic.
+
+Remote data is always landed in local memory by the collective before a kernel reads it; ordering is
+by stream events only (no device-side waiting).  CPU tensors with the gloo backend run the same
+orchestration with torch's CPU SpMM, which is how the logic is tested without GPUs.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _native
+from .ops import DEFAULT_HUB_THRESHOLD, DEFAULT_WARPS, load_native
+
+
+def partition_rows(crow: torch.Tensor, parts: int) -> torch.Tensor:
+    """Boundaries b_0..b_parts of contiguous row ranges with ~nnz/parts edges each:
+    b_k = first row whose pointer is >= k*nnz/parts (int64, on the CPU)."""
+    crow = crow.to(torch.long)
+    n = crow.numel() - 1
+    base = int(crow[0])
+    nnz = int(crow[-1]) - base
+    targets = torch.tensor([base + (k * nnz) // parts for k in range(parts + 1)], dtype=torch.long,
+                           device=crow.device)
+    bounds = torch.searchsorted(crow.contiguous(), targets, right=False).clamp_(0, n).cpu()
+    bounds[0], bounds[-1] = 0, n
+    return torch.cummax(bounds, 0).values
+
+
+@dataclass
+class ColumnBlock:
+    """The edges of a shard whose columns belong to one owner rank, as a CSR over the shard's rows.
+    Column ids stay global (they index the gathered X)."""
+
+    owner: int
+    crow: torch.Tensor
+    col: torch.Tensor
+    val: Optional[torch.Tensor]
+    workspace: Optional[torch.Tensor] = None
+    plan_ready: bool = False
+
+
+@dataclass
+class RowShard:
+    rank: int
+    world: int
+    bounds: torch.Tensor          # int64[world + 1], CPU
+    crow: torch.Tensor            # local row pointers, rebased to 0
+    col: torch.Tensor             # global column ids
+    val: Optional[torch.Tensor]
+    blocks: list[ColumnBlock] = field(default_factory=list)
+
+    @property
+    def row_begin(self) -> int:
+        return int(self.bounds[self.rank])
+
+    @property
+    def row_end(self) -> int:
+        return int(self.bounds[self.rank + 1])
+
+    @property
+    def n_local(self) -> int:
+        return self.row_end - self.row_begin
+
+    @property
+    def n_global(self) -> int:
+        return int(self.bounds[-1])
+
+
+def split_columns_by_owner(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor],
+                           bounds: torch.Tensor) -> list[ColumnBlock]:
+    """Stable partition of a CSR's edges by owner(col) = k with bounds[k] <= col < bounds[k+1]; edge
+    order inside a (row, owner) pair is preserved."""
+    world = bounds.numel() - 1
+    n_local = crow.numel() - 1
+    device = col.device
+    cuts = bounds[1:-1].to(device)
+    owner = torch.bucketize(col, cuts, right=True) if world > 1 else torch.zeros_like(col)
+    degrees = crow[1:] - crow[:-1]
+    rows = torch.repeat_interleave(torch.arange(n_local, device=device, dtype=torch.long), degrees)
+    order = torch.argsort(owner * max(n_local, 1) + rows, stable=True)
+    owner_sorted = owner[order]
+    per_owner = torch.bincount(owner_sorted, minlength=world).cpu().tolist()
+    blocks: list[ColumnBlock] = []
+    start = 0
+    for k in range(world):
+        stop = start + per_owner[k]
+        picked = order[start:stop]
+        counts = torch.bincount(rows[picked], minlength=n_local)
+        block_crow = torch.zeros(n_local + 1, dtype=torch.long, device=device)
+        torch.cumsum(counts, 0, out=block_crow[1:])
+        blocks.append(ColumnBlock(k, block_crow, col[picked].contiguous(),
+                                  None if val is None else val[picked].contiguous()))
+        start = stop
+    return blocks
+
+
+def shard_csr(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor], rank: int, world: int,
+              bounds: Optional[torch.Tensor] = None, device: Optional[torch.device] = None) -> RowShard:
+    """Cut rank ``rank``'s rows out of a full CSR (on any device) and build its column blocks."""
+    bounds = partition_rows(crow, world) if bounds is None else bounds
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    first, last = int(crow[lo]), int(crow[hi])
+    local_crow = (crow[lo:hi + 1] - crow[lo]).to(torch.long)
+    local_col = col[first:last]
+    local_val = None if val is None else val[first:last]
+    if device is not None:
+        local_crow, local_col = local_crow.to(device), local_col.to(device)
+        local_val = None if local_val is None else local_val.to(device)
+    local_crow, local_col = local_crow.contiguous(), local_col.contiguous()
+    local_val = None if local_val is None else local_val.contiguous()
+    shard = RowShard(rank, world, bounds, local_crow, local_col, local_val)
+    shard.blocks = split_columns_by_owner(local_crow, local_col, local_val, bounds)
+    return shard
+
+
+def exchange_schedule(rank: int, world: int) -> list[tuple[int, int]]:
+    """(send_to, receive_from) for steps 1..world-1: every rank sends and receives exactly one shard
+    per step and all links of the switch are busy at once."""
+    return [((rank - s) % world, (rank + s) % world) for s in range(1, world)]
+
+
+def _block_spmm(block: ColumnBlock, x_full: torch.Tensor, y: torch.Tensor, accumulate: bool, *, feature_tile: int,
+                warps: int, threshold: int) -> None:
+    if y.is_cuda:
+        if block.workspace is None:
+            block.workspace = torch.empty(_native.workspace_bytes(y.size(0)), dtype=torch.uint8, device=y.device)
+            block.plan_ready = False
+        flags = (_native.FLAG_ACCUMULATE if accumulate else 0) | (_native.FLAG_PLAN_READY if block.plan_ready else 0)
+        _native.spmm(block.crow, block.col, block.val, x_full, y, feature_tile=feature_tile, warps=warps,
+                     threshold=threshold, flags=flags, workspace=block.workspace)
+        block.plan_ready = True
+        return
+    weights = torch.ones(block.col.numel(), dtype=x_full.dtype) if block.val is None else block.val.to(x_full.dtype)
+    matrix = torch.sparse_csr_tensor(block.crow, block.col, weights, size=(y.size(0), x_full.size(0)), dtype=x_full.dtype)
+    product = torch.sparse.mm(matrix, x_full)
+    if accumulate:
+        y.add_(product)
+    else:
+        y.copy_(product)
+
+
+class ShardedSpmm:
+    """Holds the gathered-X buffer, the communication stream and the per-block plans of one shard."""
+
+    def __init__(self, shard: RowShard, features: int, *, group=None, dtype=torch.float32, feature_tile: int = 128,
+                 warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD) -> None:
+        self.shard = shard
+        self.group = group
+        self.features = features
+        self.feature_tile, self.warps, self.threshold = feature_tile, warps, threshold
+        device = shard.crow.device
+        self.device = device
+        if device.type == "cuda" and not load_native():
+            raise RuntimeError("libautosage_b200.so is required for the CUDA path")
+        self.x_full = torch.empty(shard.n_global, features, dtype=dtype, device=device)
+        self.comm_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+
+    @property
+    def x_local(self) -> torch.Tensor:
+        """View of the rank's own rows inside the gathered buffer: write the shard's features here."""
+        return self.x_full[self.shard.row_begin:self.shard.row_end]
+
+    def _shard_view(self, owner: int) -> torch.Tensor:
+        b = self.shard.bounds
+        return self.x_full[int(b[owner]):int(b[owner + 1])]
+
+    def _start_exchange(self) -> list[tuple[int, list]]:
+        shard = self.shard
+        steps: list[tuple[int, list]] = []
+        for send_to, recv_from in exchange_schedule(shard.rank, shard.world):
+            ops = [dist.P2POp(dist.isend, self.x_local, send_to, group=self.group),
+                   dist.P2POp(dist.irecv, self._shard_view(recv_from), recv_from, group=self.group)]
+            steps.append((recv_from, dist.batch_isend_irecv(ops)))
+        return steps
+
+    def forward(self, out: Optional[torch.Tensor] = None, overlap: bool = True) -> torch.Tensor:
+        """y_local = A_local @ gather(X).  ``x_local`` must already hold this rank's features."""
+        shard = self.shard
+        y = out if out is not None else torch.empty(shard.n_local, self.features, dtype=self.x_full.dtype,
+                                                    device=self.device)
+        kw = dict(feature_tile=self.feature_tile, warps=self.warps, threshold=self.threshold)
+        if shard.world == 1:
+            _block_spmm(shard.blocks[0], self.x_full, y, False, **kw)
+            return y
+        if self.comm_stream is not None:
+            current = torch.cuda.current_stream(self.device)
+            self.comm_stream.wait_stream(current)
+            with torch.cuda.stream(self.comm_stream):
+                steps = self._start_exchange()
+        else:
+            steps = self._start_exchange()
+        if not overlap:
+            for _, works in steps:
+                for work in works:
+                    work.wait()
+        _block_spmm(shard.blocks[shard.rank], self.x_full, y, False, **kw)
+        for owner, works in steps:
+            if overlap:
+                for work in works:
+                    work.wait()  # CUDA: the current stream waits for the collective, the host does not
+            _block_spmm(shard.blocks[owner], self.x_full, y, True, **kw)
+        return y
+
+
+class ShardedAutoSAGEConv(torch.nn.Module):
+    """AutoSAGEConv over a row shard: gathered aggregation, then the layer's Linear on local rows."""
+
+    def __init__(self, shard: RowShard, in_channels: int, out_channels: int, *, bias: bool = True, group=None,
+                 feature_tile: int = 128, warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD) -> None:
+        super().__init__()
+        self.linear = torch.nn.Linear(in_channels, out_channels, bias=bias)
+        self.spmm = ShardedSpmm(shard, in_channels, group=group, feature_tile=feature_tile, warps=warps,
+                                threshold=threshold)
+
+    def forward(self, x_local: Optional[torch.Tensor] = None, overlap: bool = True) -> torch.Tensor:
+        if x_local is not None and x_local.data_ptr() != self.spmm.x_local.data_ptr():
+            self.spmm.x_local.copy_(x_local)
+        aggregated = self.spmm.forward(overlap=overlap)
+        return self.linear(aggregated)
