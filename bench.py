@@ -425,9 +425,9 @@ def main() -> None:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--workload", default=None)
     parser.add_argument("--features", type=int, default=128)
-    parser.add_argument("--tile", type=int, default=128)
-    parser.add_argument("--warps", type=int, default=8)
-    parser.add_argument("--hub-threshold", type=int, default=1566)
+    parser.add_argument("--tile", type=int, default=None)
+    parser.add_argument("--warps", type=int, default=4)
+    parser.add_argument("--hub-threshold", type=int, default=1024)
     parser.add_argument("--cpu-sample-nnz", type=int, default=4_000_000)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
@@ -435,6 +435,10 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     if args.workload is None:
         args.workload = "c2_spmm" if max(args.gpus, world) == 1 else "c5_spmm"
+    if args.tile is None:
+        # X of configuration 2 is about the size of L2: 64-wide tiles keep the gathered slice
+        # resident; configuration 5's X is ten times L2 and whole 128-float rows stream best.
+        args.tile = 128 if args.workload == "c5_spmm" else 64
 
     if args.impl == "reference":
         if rank == 0:
