@@ -46,6 +46,8 @@ SIGNATURES = {
     "asg_csr_row_softmax": (_INT, [_P, _P, _P, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_csr_attention": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _F32, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_workspace_status": (_INT, [_P, _P, _P]),
+    "asg_spmm_csr_split_noalloc": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _P]),
+    "asg_static_max_rows": (_I64, []),
 }
 
 _LIB: Optional[ctypes.CDLL] = None

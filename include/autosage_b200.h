@@ -148,6 +148,33 @@ int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, c
  */
 int asg_workspace_status(const void* workspace, int32_t* host_status, void* stream);
 
+/*
+ * SpMM that allocates nothing (no counterpart in the reference, whose operators always allocate
+ * through ATen).  Same arguments and results as asg_spmm_csr_split, minus the workspace: the
+ * scratch (row order of the plan, work counters) is a fixed array built into the library's device
+ * image, about 4.4 MB on every GPU that loads the library, kept until the process exits.
+ *
+ * Meant for callers that cannot obtain device memory where they call from - a host whose
+ * allocator is frozen after start-up, a callback of another runtime in which cudaMalloc is
+ * forbidden or would stall the device, a language binding without a device allocator.
+ *
+ *   - n_rows may be at most asg_static_max_rows() (1,048,576); larger graphs are rejected with
+ *     ASG_ERANGE and a message naming the limit.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *     with that device current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array and each call rebuilds its contents from scratch,
+ *     so nothing needs clearing between calls - but two calls that overlap on the GPU (different
+ *     streams, or different host threads) race on it.  Issue them on one stream, or serialise them.
+ *   - No cudaMalloc, cudaFree or other allocating routine is called.
+ */
+int asg_spmm_csr_split_noalloc(const int64_t* crow, const int64_t* col, const float* val,
+                               const float* x, float* y, int64_t n_rows, int64_t nnz, int64_t f,
+                               int feature_tile, int warps_per_block, int64_t hub_threshold,
+                               void* stream);
+
+/* Largest n_rows asg_spmm_csr_split_noalloc accepts. */
+int64_t asg_static_max_rows(void);
+
 #ifdef __cplusplus
 }
 #endif
