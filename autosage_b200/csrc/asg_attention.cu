@@ -155,7 +155,7 @@ __device__ __forceinline__ void attention_batches(const AttentionArgs& a, int ro
     float part[G];
 #pragma unroll
     for (int i = 0; i < G; ++i) part[i] = 0.f;
-    batch_dots<VW, G, NV, U>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
+    batch_dots<VW, G, NV, U, true>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
     const float dot = group_reduce_scatter<G>(part, l);
     const int my_edge = l * EPI + sub;
     const float score = my_edge < cnt ? dot * a.scale : -CUDART_INF_F;
@@ -203,8 +203,13 @@ __device__ __forceinline__ void attention_batches(const AttentionArgs& a, int ro
   }
 }
 
+#ifdef ASG_ATTN_MIN_BLOCKS  // e.g. 2 caps the kernel at 64 registers per thread
+#define ASG_BOUNDS __launch_bounds__(512, ASG_ATTN_MIN_BLOCKS)
+#else
+#define ASG_BOUNDS __launch_bounds__(512)
+#endif
 template <int VW, int G, int NV, int U>
-__global__ void __launch_bounds__(512) attention_kernel(const AttentionArgs a) {
+__global__ void ASG_BOUNDS attention_kernel(const AttentionArgs a) {
   constexpr int FT = VW * G * NV;
   extern __shared__ __align__(16) unsigned char smem[];
   int* s_item = reinterpret_cast<int*>(smem);

@@ -64,11 +64,11 @@ __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, l
 #pragma unroll
     for (int i = 0; i < G; ++i) part[i] = 0.f;
     if (a.n_tiles == 1) {
-      batch_dots<VW, G, NV, U>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
+      batch_dots<VW, G, NV, U, false>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
     } else {
       for (int tile = 0; tile < a.n_tiles; ++tile) {
         load_q(tile);
-        batch_dots<VW, G, NV, U>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
+        batch_dots<VW, G, NV, U, false>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
       }
     }
     const float dot = group_reduce_scatter<G>(part, l);
@@ -77,8 +77,13 @@ __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, l
   }
 }
 
+#ifdef ASG_SDDMM_MIN_BLOCKS  // e.g. 2 caps the kernel at 64 registers per thread
+#define ASG_BOUNDS __launch_bounds__(512, ASG_SDDMM_MIN_BLOCKS)
+#else
+#define ASG_BOUNDS __launch_bounds__(512)
+#endif
 template <int VW, int G, int NV, int U>
-__global__ void __launch_bounds__(512) sddmm_kernel(const SddmmArgs a) {
+__global__ void ASG_BOUNDS sddmm_kernel(const SddmmArgs a) {
   __shared__ int s_item;
   const int tid = threadIdx.x;
   const int lane = tid & 31;

@@ -36,7 +36,7 @@ struct SpmmArgs {
 constexpr int kChunkPerWarp = 128;  // staged edges per warp and stage in the hub path
 
 template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL>
-__global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
+__device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
   constexpr int U = U_REQUESTED < G ? U_REQUESTED : G;  // an unrolled batch never exceeds 32 edges
   constexpr int EPI = 32 / G;          // edges per load instruction
   constexpr int FT = VW * G * NV;      // feature tile
@@ -105,6 +105,8 @@ __global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
         fvalid[v] = foff[v] < f;
       }
 
+      const bool hub_tile_full = fbase + FT <= f;
+
       // stage one chunk [g0, g1) of col/val into stage `st`
       auto stage_chunk = [&](int k, unsigned sq) {
         const int st = sq & 1;
@@ -160,6 +162,26 @@ __global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
           for (int b = warp; b < n_batches; b += n_warps) {
             float xv[U][NV][VW];
             float wu[U];
+            if ((b + 1) * BU <= cnt && hub_tile_full) {
+              // whole batch inside the chunk and the feature tile: no predicates, no zero fill
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                const int j = b * BU + u * EPI + sub;
+                const int c = static_cast<int>(ccol[j]);
+                if (HAS_VAL) wu[u] = cval[j];
+                const float* xrow = a.x + static_cast<long long>(c) * f;
+#pragma unroll
+                for (int v = 0; v < NV; ++v) VecIO<VW>::load(xv[u][v], xrow + foff[v], pol_keep);
+              }
+#pragma unroll
+              for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int v = 0; v < NV; ++v)
+#pragma unroll
+                  for (int i = 0; i < VW; ++i)
+                    acc[v][i] = HAS_VAL ? fmaf(wu[u], xv[u][v][i], acc[v][i]) : acc[v][i] + xv[u][v][i];
+              continue;
+            }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
               const int j = b * BU + u * EPI + sub;
@@ -256,6 +278,8 @@ __global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
         fvalid[v] = foff[v] < f;
       }
 
+      const bool tile_full = fbase + FT <= f;
+
       int c_next = 0;
       float w_next = 0.f;
       if (s + lane < e) {
@@ -269,6 +293,31 @@ __global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
         if (p + 32 + lane < e) {
           c_next = static_cast<int>(ld_index(a.col + p + 32 + lane, pol_stream));
           if (HAS_VAL) w_next = ld_weight(a.val + p + 32 + lane, pol_stream);
+        }
+        if (cnt == 32 && tile_full) {
+          // Common case: a full batch inside a full feature tile needs no predicates or zero fill.
+#pragma unroll 1
+          for (int j = 0; j < 32; j += BU) {
+            float xv[U][NV][VW];
+            float wu[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int src = j + u * EPI + sub;
+              const int c = __shfl_sync(kFull, c_l, src);
+              if (HAS_VAL) wu[u] = __shfl_sync(kFull, w_l, src);
+              const float* xrow = a.x + static_cast<long long>(c) * f;
+#pragma unroll
+              for (int v = 0; v < NV; ++v) VecIO<VW>::load(xv[u][v], xrow + foff[v], pol_keep);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+              for (int v = 0; v < NV; ++v)
+#pragma unroll
+                for (int i = 0; i < VW; ++i)
+                  acc[v][i] = HAS_VAL ? fmaf(wu[u], xv[u][v][i], acc[v][i]) : acc[v][i] + xv[u][v][i];
+          }
+          continue;
         }
         for (int j = 0; j < cnt; j += BU) {
           float xv[U][NV][VW];
@@ -325,13 +374,28 @@ __global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
   }
 }
 
+// Two entry kernels over the same body.  They differ only in the register budget the compiler is
+// given: with launch bounds (512) alone it keeps registers low for occupancy (best when the gather
+// is served by L2); with (512, 1) it may use 128 registers and schedules loads further ahead, which
+// measured 10 % faster when the gathered rows come from HBM (whole-row 128-float tiles).
+template <int VW, int G, int NV, int U, bool HAS_VAL>
+__global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
+  spmm_body<VW, G, NV, U, HAS_VAL>(a);
+}
+template <int VW, int G, int NV, int U, bool HAS_VAL>
+__global__ void __launch_bounds__(512, 1) spmm_kernel_deep(const SpmmArgs a) {
+  spmm_body<VW, G, NV, U, HAS_VAL>(a);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------------
 template <int VW, int G, int NV, int U, bool HAS_VAL>
 static int launch_instance(const SpmmArgs& args, int warps, cudaStream_t stream, int device) {
   constexpr int FT = VW * G * NV;
-  auto kernel = spmm_kernel<VW, G, NV, U, HAS_VAL>;
+  // whole-row tiles of 128 floats with 256-bit loads are the HBM-streaming configuration
+  constexpr bool kDeep = (VW == 8 && FT == 128);
+  auto kernel = kDeep ? spmm_kernel_deep<VW, G, NV, U, HAS_VAL> : spmm_kernel<VW, G, NV, U, HAS_VAL>;
   const int threads = warps * 32;
   const int chunk = kChunkPerWarp * warps;
   const size_t smem = 128 + size_t(24) * chunk + size_t(4) * warps * FT;

@@ -116,25 +116,27 @@ namespace asg {
 // Lane `lane` holds in c_l the column index of edge `lane` of the batch; `cnt` edges are valid.
 // Load instruction i (0 <= i < G) serves edges i*EPI + sub, one per lane group; its partial dot
 // product is added to part[i].  U instructions are issued before their results are used.
-template <int VW, int G, int NV, int U>
-__device__ __forceinline__ void batch_dots(const float* __restrict__ mat, int f, int c_l, int cnt, int sub,
-                                           const float (&q)[NV][VW], const bool (&fvalid)[NV],
-                                           const int (&foff)[NV], uint64_t pol, float (&part)[G]) {
+// CHECKED = false is the fast form for a full batch (cnt == 32) inside a full feature tile: no
+// predicates and no zero fill.
+template <int VW, int G, int NV, int U, bool CHECKED>
+__device__ __forceinline__ void batch_dots_impl(const float* __restrict__ mat, int f, int c_l, int cnt, int sub,
+                                                const float (&q)[NV][VW], const bool (&fvalid)[NV],
+                                                const int (&foff)[NV], uint64_t pol, float (&part)[G]) {
   constexpr int EPI = 32 / G;
   constexpr int UU = U < G ? U : G;
 #pragma unroll
   for (int i0 = 0; i0 < G; i0 += UU) {
-    if (i0 * EPI < cnt) {
+    if (!CHECKED || i0 * EPI < cnt) {
       float kv[UU][NV][VW];
 #pragma unroll
       for (int u = 0; u < UU; ++u) {
         const int src = (i0 + u) * EPI + sub;
         const int c = __shfl_sync(kFull, c_l, src);
-        const bool ok = src < cnt;
+        const bool ok = !CHECKED || src < cnt;
         const float* krow = mat + static_cast<size_t>(c) * f;
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-          if (ok && fvalid[v]) {
+          if (!CHECKED || (ok && fvalid[v])) {
             VecIO<VW>::load(kv[u][v], krow + foff[v], pol);
           } else {
 #pragma unroll
@@ -152,6 +154,26 @@ __device__ __forceinline__ void batch_dots(const float* __restrict__ mat, int f,
         part[i0 + u] += d;
       }
     }
+  }
+}
+
+// FAST_PATH adds the unchecked form for full batches; it costs registers (occupancy), which pays
+// in the attention kernel but not in the SDDMM kernel (measured), so the caller chooses.
+template <int VW, int G, int NV, int U, bool FAST_PATH>
+__device__ __forceinline__ void batch_dots(const float* __restrict__ mat, int f, int c_l, int cnt, int sub,
+                                           const float (&q)[NV][VW], const bool (&fvalid)[NV],
+                                           const int (&foff)[NV], uint64_t pol, float (&part)[G]) {
+  if (!FAST_PATH) {
+    batch_dots_impl<VW, G, NV, U, true>(mat, f, c_l, cnt, sub, q, fvalid, foff, pol, part);
+    return;
+  }
+  bool lane_full = true;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) lane_full = lane_full && fvalid[v];
+  if (cnt == 32 && __all_sync(kFull, lane_full)) {
+    batch_dots_impl<VW, G, NV, U, false>(mat, f, c_l, cnt, sub, q, fvalid, foff, pol, part);
+  } else {
+    batch_dots_impl<VW, G, NV, U, true>(mat, f, c_l, cnt, sub, q, fvalid, foff, pol, part);
   }
 }
 

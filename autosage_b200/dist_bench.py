@@ -35,7 +35,18 @@ def run(args):
         raise RuntimeError(f"--gpus {args.gpus} needs torch.distributed.run with {args.gpus} ranks (got {world})")
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
-    dist.init_process_group("nccl", device_id=device)
+    multi = world > 1
+    if multi:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if multi:
+            dist.barrier()
+
+    def reduce_max(t):
+        if multi:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t
     if not autosage_b200.load_native():
         raise RuntimeError(f"libautosage_b200.so failed to load: {autosage_b200.ops.native_load_error()}")
 
@@ -45,6 +56,30 @@ def run(args):
     n, nnz = info["rows"], info["nnz"]
     bounds = asg_dist.partition_rows(crow, world)
     shard = asg_dist.shard_csr(crow, col, None, rank, world, bounds)
+
+    # The same layer on ONE GPU (no sharding, no exchange), timed inside this job so that every
+    # multi-GPU line carries its own strong-scaling reference.  Every rank times it on its own GPU
+    # at the same moment; the maximum over ranks is reported.
+    single_ms = None
+    if multi:
+        torch.manual_seed(0)
+        whole = asg_dist.shard_csr(crow, col, None, 0, 1, asg_dist.partition_rows(crow, 1))
+        solo = asg_dist.ShardedAutoSAGEConv(whole, f, out_f, bias=True, feature_tile=args.tile, warps=args.warps,
+                                            threshold=args.hub_threshold).to(device)
+        solo.spmm.x_local.normal_(generator=torch.Generator(device=device).manual_seed(3))
+        with torch.no_grad():
+            for _ in range(3):
+                solo()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = max(3, min(args.steps, 5))
+            t0.record()
+            for _ in range(reps):
+                solo()
+            t1.record()
+            torch.cuda.synchronize()
+        single_ms = float(reduce_max(torch.tensor([t0.elapsed_time(t1) / reps], device=device)).item())
+        del solo, whole
     del crow, col
     torch.cuda.empty_cache()
 
@@ -69,7 +104,7 @@ def run(args):
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
-    dist.barrier()
+    barrier()
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with bench.ClockSampler(local_rank) as clocks:
@@ -78,11 +113,52 @@ def run(args):
             step()
         end.record(stream)
         torch.cuda.synchronize()
-        dist.barrier()
+        barrier()
         torch.cuda.synchronize()
-    elapsed = torch.tensor([begin.elapsed_time(end)], device=device)
-    dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    elapsed = reduce_max(torch.tensor([begin.elapsed_time(end)], device=device))
     ms_per_step = float(elapsed.item()) / args.steps
+
+    # where the step goes (separate, untimed-for-the-metric runs): exchange alone, the column-block
+    # SpMMs alone (no exchange), the Linear alone; maxima over ranks
+    def timed(fn, reps=5):
+        fn()
+        torch.cuda.synchronize()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        barrier()
+        return float(reduce_max(torch.tensor([a.elapsed_time(b) / reps], device=device)).item())
+
+    def exchange_only():
+        if not multi:
+            return
+        layer.spmm.comm_stream.wait_stream(stream)
+        with torch.cuda.stream(layer.spmm.comm_stream):
+            steps = layer.spmm._start_exchange()
+        for _, works in steps:
+            for work in works:
+                work.wait()
+
+    def compute_only():
+        kw = dict(feature_tile=args.tile, warps=args.warps, threshold=args.hub_threshold)
+        y = aggregated_scratch
+        asg_dist._block_spmm(shard.blocks[shard.rank], layer.spmm.x_full, y, False, **kw)
+        for k in range(world):
+            if k != shard.rank:
+                asg_dist._block_spmm(shard.blocks[k], layer.spmm.x_full, y, True, **kw)
+
+    aggregated_scratch = torch.empty(shard.n_local, f, device=device)
+    with torch.no_grad():
+        breakdown = {
+            "exchange_ms": round(timed(exchange_only), 4),
+            "block_spmm_ms": round(timed(compute_only), 4),
+            "linear_ms": round(timed(lambda: layer.linear(aggregated_scratch)), 4),
+        }
+    del aggregated_scratch
 
     # end to end: X shard from pinned host memory in, output shard back to the host, every step
     out_host = torch.empty(shard.n_local, out_f).pin_memory()
@@ -93,22 +169,24 @@ def run(args):
 
     e2e_step()
     torch.cuda.synchronize()
-    dist.barrier()
+    barrier()
     e2e_steps = max(2, min(args.steps, 5))
     begin.record(stream)
     for _ in range(e2e_steps):
         e2e_step()
     end.record(stream)
     torch.cuda.synchronize()
-    dist.barrier()
-    e2e_elapsed = torch.tensor([begin.elapsed_time(end)], device=device)
-    dist.all_reduce(e2e_elapsed, op=dist.ReduceOp.MAX)
+    barrier()
+    e2e_elapsed = reduce_max(torch.tensor([begin.elapsed_time(end)], device=device))
     e2e_ms = float(e2e_elapsed.item()) / e2e_steps
     io_bytes = torch.tensor([x_shard_host.numel() * 4, out_host.numel() * 4], device=device, dtype=torch.long)
-    dist.all_reduce(io_bytes)
     local_nnz = torch.tensor([shard.col.numel()], device=device, dtype=torch.long)
     gathered = [torch.zeros_like(local_nnz) for _ in range(world)]
-    dist.all_gather(gathered, local_nnz)
+    if multi:
+        dist.all_reduce(io_bytes)
+        dist.all_gather(gathered, local_nnz)
+    else:
+        gathered = [local_nnz]
 
     algorithmic = conv_bytes(n, nnz, f, out_f)
     value = algorithmic / (ms_per_step * 1e-3) / 1e9
@@ -141,6 +219,9 @@ def run(args):
             "edges_f_per_s": round(nnz * f / (ms_per_step * 1e-3), 1),
             "algorithmic_bytes_per_step": algorithmic,
             "nvlink_receive_bytes_per_gpu": 4 * (n - shard.n_local) * f,
+            "breakdown_ms": breakdown,
+            "single_gpu_ms_per_step": None if single_ms is None else round(single_ms, 4),
+            "speedup_vs_1gpu_same_workload": None if single_ms is None else round(single_ms / ms_per_step, 3),
             "roofline": {
                 "bound": "hbm",
                 "kernel": "spmm_kernel (per GPU share of the step)",
@@ -162,6 +243,7 @@ def run(args):
             "gpu_launches": args.steps * world * world,
             "clocks": clocks.summary(),
         }
-    dist.barrier()
-    dist.destroy_process_group()
+    if multi:
+        dist.barrier()
+        dist.destroy_process_group()
     return line

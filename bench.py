@@ -1,7 +1,7 @@
 """Benchmark of the sparse hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c2_spmm|c3_sddmm|c4_attention|c5_spmm] [--features F]
+                    [--workload c2_spmm|c3_sddmm|c4_attention|c5_spmm|c5_conv] [--features F]
 
 One "step" is one pass of the hot path (one SpMM / SDDMM / attention call) over the whole synthetic
 graph.  Metric: algorithmic GB/s (bytes = CSR + gathered dense rows + output, the byte model of the
@@ -367,13 +367,15 @@ def run_reference(args) -> dict:
     restated in oracle/) on this host's cores; each step is one call on a bounded row sample."""
     from autosage_b200 import synthetic as syn
 
-    spec = syn.REDDIT_LIKE if args.workload != "c5_spmm" else syn.PRODUCTS_LIKE
+    # torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    spec = syn.REDDIT_LIKE if not args.workload.startswith("c5") else syn.PRODUCTS_LIKE
     # Only the sampled rows are materialised on the host: same degree sequence as the GPU arm's
     # graph, columns iid uniform over all N columns and sorted inside each row.
     degree, _ = syn.powerlaw_degrees(spec.rows, spec.target_nnz, spec.alpha, spec.max_degree, 0)
     n, f = spec.rows, args.features
     info = {"rows": n, "nnz": int(degree.sum())}
-    weighted = args.workload != "c5_spmm"
+    weighted = not args.workload.startswith("c5")
     from oracle import oracle
 
     crow = torch.zeros(n + 1, dtype=torch.long)
@@ -434,17 +436,17 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if args.workload is None:
-        args.workload = "c2_spmm" if max(args.gpus, world) == 1 else "c5_spmm"
+        args.workload = "c2_spmm" if max(args.gpus, world) == 1 else "c5_conv"
     if args.tile is None:
         # X of configuration 2 is about the size of L2: 64-wide tiles keep the gathered slice
         # resident; configuration 5's X is ten times L2 and whole 128-float rows stream best.
-        args.tile = 128 if args.workload == "c5_spmm" else 64
+        args.tile = 128 if args.workload.startswith("c5") else 64
 
     if args.impl == "reference":
         if rank == 0:
             print(json.dumps(run_reference(args)), flush=True)
         return
-    if world > 1 or args.gpus > 1:
+    if world > 1 or args.gpus > 1 or args.workload == "c5_conv":
         from autosage_b200 import dist_bench
 
         line = dist_bench.run(args)
