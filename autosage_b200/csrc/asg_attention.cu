@@ -116,92 +116,110 @@ struct AttentionArgs {
   float scale;
 };
 
-// Online-softmax state of one warp for one row: running max m, running sum l and the output
-// accumulator (lane-group partial sums of the feature tile).
+// Loads the row of Q a warp works on into registers (lane l of a group owns floats VW*(l+G*v)+i).
+template <int VW, int G, int NV>
+__device__ __forceinline__ void attention_load_q(const AttentionArgs& a, int row, int lane, uint64_t pol_stream,
+                                                 float (&q)[NV][VW], bool (&fvalid)[NV], int (&foff)[NV]) {
+  const int l = lane % G;
+  const float* qrow = a.q + static_cast<size_t>(row) * a.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    foff[v] = VW * (l + G * v);
+    fvalid[v] = foff[v] < a.f;
+    if (fvalid[v]) {
+      VecIO<VW>::load(q[v], qrow + foff[v], pol_stream);  // read once: must not push K and V out of L2
+    } else {
+#pragma unroll
+      for (int i = 0; i < VW; ++i) q[v][i] = 0.f;
+    }
+  }
+}
+
+// One batch of up to 32 edges (column ids in c_l, one per lane) folded into the online-softmax state
+// of the row: running max m, running sum l and the output accumulator (lane-group partial sums).
 template <int VW, int G, int NV, int U_REQUESTED>
-__device__ __forceinline__ void attention_batches(const AttentionArgs& a, int row, long long first, long long stride,
-                                                  int lane, uint64_t pol_keep, uint64_t pol_stream, float& m_run,
-                                                  float& l_run, float (&acc)[NV][VW]) {
+__device__ __forceinline__ void attention_one_batch(const AttentionArgs& a, int c_l, int cnt, int lane,
+                                                    const float (&q)[NV][VW], const bool (&fvalid)[NV],
+                                                    const int (&foff)[NV], uint64_t pol_keep, float& m_run,
+                                                    float& l_run, float (&acc)[NV][VW]) {
   constexpr int EPI = 32 / G;
   constexpr int U = U_REQUESTED < G ? U_REQUESTED : G;  // an unrolled batch never exceeds 32 edges
   constexpr int BU = EPI * U;
   const int l = lane % G;
   const int sub = lane / G;
   const int f = a.f;
-  const long long e = a.crow[row + 1];
-  const float* qrow = a.q + static_cast<size_t>(row) * f;
 
+  // 1. scores of the batch: lane (l, sub) ends with the score of edge l*EPI + sub
+  float part[G];
+#pragma unroll
+  for (int i = 0; i < G; ++i) part[i] = 0.f;
+  batch_dots<VW, G, NV, U, true>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
+  const float dot = group_reduce_scatter<G>(part, l);
+  const int my_edge = l * EPI + sub;
+  const float score = my_edge < cnt ? dot * a.scale : -CUDART_INF_F;
+
+  // 2. fold into the running max / sum
+  const float m_new = fmaxf(m_run, warp_max(score));
+  const float rescale = expf(m_run - m_new);  // exp(-inf) = 0 on the first batch
+  const float prob = my_edge < cnt ? expf(score - m_new) : 0.f;
+  l_run = l_run * rescale + warp_sum(prob);
+  m_run = m_new;
+#pragma unroll
+  for (int v = 0; v < NV; ++v)
+#pragma unroll
+    for (int i = 0; i < VW; ++i) acc[v][i] *= rescale;
+
+  // 3. acc += sum_j prob_j * V[col_j]; the probability of edge j sits in lane (j/EPI) + G*(j%EPI)
+  for (int j = 0; j < cnt; j += BU) {
+    float xv[U][NV][VW];
+    float wu[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int src = j + u * EPI + sub;
+      const int c = __shfl_sync(kFull, c_l, src);
+      const float w = __shfl_sync(kFull, prob, (src / EPI) + G * (src % EPI));
+      const bool ok = src < cnt;
+      wu[u] = ok ? w : 0.f;
+      const float* vrow = a.v + static_cast<size_t>(c) * f;
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        if (ok && fvalid[v]) {
+          VecIO<VW>::load(xv[u][v], vrow + foff[v], pol_keep);
+        } else {
+#pragma unroll
+          for (int i = 0; i < VW; ++i) xv[u][v][i] = 0.f;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int v = 0; v < NV; ++v)
+#pragma unroll
+        for (int i = 0; i < VW; ++i) acc[v][i] = fmaf(wu[u], xv[u][v][i], acc[v][i]);
+  }
+}
+
+// All batches of one row that this warp is responsible for (first, first+stride, ...).
+template <int VW, int G, int NV, int U>
+__device__ __forceinline__ void attention_batches(const AttentionArgs& a, int row, long long first, long long stride,
+                                                  int lane, uint64_t pol_keep, uint64_t pol_stream, float& m_run,
+                                                  float& l_run, float (&acc)[NV][VW]) {
+  const long long e = a.crow[row + 1];
   float q[NV][VW];
   bool fvalid[NV];
   int foff[NV];
-#pragma unroll
-  for (int v = 0; v < NV; ++v) {
-    foff[v] = VW * (l + G * v);
-    fvalid[v] = foff[v] < f;
-    if (fvalid[v]) {
-      VecIO<VW>::load_plain(q[v], qrow + foff[v]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < VW; ++i) q[v][i] = 0.f;
-    }
-  }
-
+  attention_load_q<VW, G, NV>(a, row, lane, pol_stream, q, fvalid, foff);
   for (long long p = first; p < e; p += stride) {
     const int cnt = e - p < 32 ? static_cast<int>(e - p) : 32;
     int c_l = 0;
     if (lane < cnt) c_l = static_cast<int>(ld_index(a.col + p + lane, pol_stream));
-
-    // 1. scores of the batch: lane (l, sub) ends with the score of edge l*EPI + sub
-    float part[G];
-#pragma unroll
-    for (int i = 0; i < G; ++i) part[i] = 0.f;
-    batch_dots<VW, G, NV, U, true>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
-    const float dot = group_reduce_scatter<G>(part, l);
-    const int my_edge = l * EPI + sub;
-    const float score = my_edge < cnt ? dot * a.scale : -CUDART_INF_F;
-
-    // 2. fold into the running max / sum
-    const float m_new = fmaxf(m_run, warp_max(score));
-    const float rescale = expf(m_run - m_new);  // exp(-inf) = 0 on the first batch
-    const float prob = my_edge < cnt ? expf(score - m_new) : 0.f;
-    l_run = l_run * rescale + warp_sum(prob);
-    m_run = m_new;
-#pragma unroll
-    for (int v = 0; v < NV; ++v)
-#pragma unroll
-      for (int i = 0; i < VW; ++i) acc[v][i] *= rescale;
-
-    // 3. acc += sum_j prob_j * V[col_j]; the probability of edge j sits in lane (j/EPI) + G*(j%EPI)
-    for (int j = 0; j < cnt; j += BU) {
-      float xv[U][NV][VW];
-      float wu[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int src = j + u * EPI + sub;
-        const int c = __shfl_sync(kFull, c_l, src);
-        const float w = __shfl_sync(kFull, prob, (src / EPI) + G * (src % EPI));
-        const bool ok = src < cnt;
-        wu[u] = ok ? w : 0.f;
-        const float* vrow = a.v + static_cast<size_t>(c) * f;
-#pragma unroll
-        for (int v = 0; v < NV; ++v) {
-          if (ok && fvalid[v]) {
-            VecIO<VW>::load(xv[u][v], vrow + foff[v], pol_keep);
-          } else {
-#pragma unroll
-            for (int i = 0; i < VW; ++i) xv[u][v][i] = 0.f;
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-#pragma unroll
-        for (int v = 0; v < NV; ++v)
-#pragma unroll
-          for (int i = 0; i < VW; ++i) acc[v][i] = fmaf(wu[u], xv[u][v][i], acc[v][i]);
-    }
+    attention_one_batch<VW, G, NV, U>(a, c_l, cnt, lane, q, fvalid, foff, pol_keep, m_run, l_run, acc);
   }
 }
+
+template <int VW, int G, int NV, int U>
+__device__ __forceinline__ void attention_short_rows(const AttentionArgs& a);
 
 #ifdef ASG_ATTN_MIN_BLOCKS  // e.g. 2 caps the kernel at 64 registers per thread
 #define ASG_BOUNDS __launch_bounds__(512, ASG_ATTN_MIN_BLOCKS)
@@ -280,11 +298,13 @@ __global__ void ASG_BOUNDS attention_kernel(const AttentionArgs a) {
       }
     }
   }
-  if (n_light > 0) {
+  const int n_short = a.header->n_short;
+  const int n_medium = n_light - n_short;  // light rows of 32 edges or more
+  if (n_medium > 0) {
     const int* light = a.order + n_hub;
     for (;;) {
       const unsigned long long it = warp_next(&a.header->counter[1]);
-      if (it >= static_cast<unsigned long long>(n_light)) break;
+      if (it >= static_cast<unsigned long long>(n_medium)) break;
       const int row = light[it];
       float m_run = -CUDART_INF_F, l_run = 0.f;
       float acc[NV][VW];
@@ -309,6 +329,88 @@ __global__ void ASG_BOUNDS attention_kernel(const AttentionArgs a) {
 #pragma unroll
             for (int i = 0; i < VW; ++i) r[i] = acc[v][i] * inv;
             VecIO<VW>::store(a.out + static_cast<size_t>(row) * f + fo, r);
+          }
+        }
+      }
+    }
+  }
+  attention_short_rows<VW, G, NV, U>(a);
+}
+
+// Queue 2: light rows of fewer than 32 edges.  A warp grabs 32 of them, reads ids and row pointers
+// with coalesced loads and walks them with the next row's columns already in flight; one batch per
+// row, so the online-softmax state never needs rescaling.  It stays inside the main kernel: the longest
+// hub rows keep a few CTAs busy for a long time and these rows are what the rest of the GPU does
+// meanwhile (as a kernel of its own, launched afterwards, it measured 30 % slower end to end).
+template <int VW, int G, int NV, int U>
+__device__ __forceinline__ void attention_short_rows(const AttentionArgs& a) {
+  const int lane = threadIdx.x & 31;
+  const int l = lane % G;
+  const int sub = lane / G;
+  const uint64_t pol_keep = policy_evict_last();
+  const uint64_t pol_stream = policy_evict_first();
+  const int n_hub = a.header->n_hub;
+  const int n_short = a.header->n_short;
+  const int n_medium = a.header->n_light - n_short;
+  const int f = a.f;
+  if (n_short > 0) {
+    const int* shorts = a.order + n_hub + n_medium;
+    const int n_batches = (n_short + 31) / 32;
+    for (;;) {
+      const unsigned long long it = warp_next(&a.header->counter[2]);
+      if (it >= static_cast<unsigned long long>(n_batches)) break;
+      const int first = static_cast<int>(it) * 32;
+      const int n_here = n_short - first < 32 ? n_short - first : 32;
+      int row_l = 0;
+      long long s_l = 0, e_l = 0;
+      if (lane < n_here) {
+        row_l = shorts[first + lane];
+        s_l = a.crow[row_l];
+        e_l = a.crow[row_l + 1];
+      }
+      long long s_cur = __shfl_sync(kFull, s_l, 0);
+      int cnt_cur = static_cast<int>(__shfl_sync(kFull, e_l, 0) - s_cur);
+      int c_next = 0;
+      if (lane < cnt_cur) c_next = static_cast<int>(ld_index(a.col + s_cur + lane, pol_stream));
+      for (int r = 0; r < n_here; ++r) {
+        const int row = __shfl_sync(kFull, row_l, r);
+        const int cnt = cnt_cur;
+        const int c_l = c_next;
+        if (r + 1 < n_here) {
+          s_cur = __shfl_sync(kFull, s_l, r + 1);
+          cnt_cur = static_cast<int>(__shfl_sync(kFull, e_l, r + 1) - s_cur);
+          if (lane < cnt_cur) c_next = static_cast<int>(ld_index(a.col + s_cur + lane, pol_stream));
+        }
+        float m_run = -CUDART_INF_F, l_run = 0.f;
+        float acc[NV][VW];
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
+        if (cnt > 0) {
+          float q[NV][VW];
+          bool fvalid[NV];
+          int foff[NV];
+          attention_load_q<VW, G, NV>(a, row, lane, pol_stream, q, fvalid, foff);
+          attention_one_batch<VW, G, NV, U>(a, c_l, cnt, lane, q, fvalid, foff, pol_keep, m_run, l_run, acc);
+#pragma unroll
+          for (int o = G; o < 32; o <<= 1)
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+              for (int i = 0; i < VW; ++i) acc[v][i] += __shfl_xor_sync(kFull, acc[v][i], o);
+        }
+        if (sub == 0) {
+          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+#pragma unroll
+          for (int v = 0; v < NV; ++v) {
+            const int fo = VW * (l + G * v);
+            if (fo < f) {
+              float out_v[VW];
+#pragma unroll
+              for (int i = 0; i < VW; ++i) out_v[i] = acc[v][i] * inv;
+              VecIO<VW>::store(a.out + static_cast<size_t>(row) * f + fo, out_v);
+            }
           }
         }
       }

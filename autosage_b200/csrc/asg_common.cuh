@@ -73,6 +73,7 @@ int sm_count(int device);  // cached per device (asg_api.cu)
 constexpr int kBuckets = 48;        // 24 hub buckets + 24 light buckets (by floor(log2(degree)))
 constexpr int kPlanBlock = 1024;    // rows per block of the counting sort
 constexpr int kCounters = 8;
+constexpr int kShortDegree = 32;     // rows below this degree form the "short" tail of the light class
 
 struct Header {
   int n_hub;
@@ -81,7 +82,8 @@ struct Header {
   int n_rows;
   unsigned long long counter[kCounters];  // work queues of the persistent kernels
   long long hub_threshold;
-  int reserved[42];
+  int n_short;  // light rows with fewer than kShortDegree edges: the tail of `order`, taken 32 at a time
+  int reserved[41];
 };
 static_assert(sizeof(Header) == 256, "header must stay 256 bytes");
 

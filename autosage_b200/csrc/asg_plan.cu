@@ -105,6 +105,9 @@ __global__ void __launch_bounds__(1024) plan_scan(int* __restrict__ block_hist, 
     if (length > 0) n_hub = first_light < length ? block_hist[first_light] : n_rows;
     header->n_hub = n_hub;
     header->n_light = n_rows - n_hub;
+    // light rows with degree < 32 have 1 + floor(log2 degree) <= 5, i.e. light buckets 24 + (23 - 5) = 42 .. 47
+    const long long first_short = 42ll * n_blocks;
+    header->n_short = length > 0 ? n_rows - block_hist[first_short] : 0;
     header->status = 0;
     header->n_rows = n_rows;
     header->hub_threshold = threshold;

@@ -47,7 +47,7 @@ __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, l
       foff[v] = tile * FT + VW * (l + G * v);
       fvalid[v] = foff[v] < f;
       if (fvalid[v]) {
-        VecIO<VW>::load_plain(q[v], qrow + foff[v]);
+        VecIO<VW>::load(q[v], qrow + foff[v], pol_stream);  // read once: must not push K out of L2
       } else {
 #pragma unroll
         for (int i = 0; i < VW; ++i) q[v][i] = 0.f;

@@ -1,4 +1,6 @@
-// CSR SpMM for sm_100a: one persistent kernel that drains two work queues built by the plan.
+// CSR SpMM for sm_100a: persistent kernels that drain three work queues built by the plan: the main
+// kernel takes queues 0 and 1 below, a second small kernel takes queue 2 (light rows of fewer than
+// 32 edges, 32 rows per grab; see spmm_short_rows).
 //
 //   queue 0  hub rows (degree >= threshold): one CTA per (hub row, feature tile).  The row's
 //            col/val segment is staged into shared memory in chunks by 1-D bulk async copies (TMA
@@ -34,6 +36,133 @@ struct SpmmArgs {
 };
 
 constexpr int kChunkPerWarp = 128;  // staged edges per warp and stage in the hub path
+
+// Queue 2: light rows of fewer than 32 edges, taken 32 rows per grab.  Rows that short are
+// latency-bound when taken one at a time (queue grab, row id, two row pointers, columns, X rows,
+// output: five dependent memory round trips for a handful of edges).  Here a warp reads the ids
+// and pointers of 32 rows with one coalesced load each and walks them with the next row's columns
+// already in flight.  It runs as a kernel of its own (launched right after the main one) so that its
+// registers and schedule do not disturb the long-row loops: inlined into the main kernel it cost the
+// long-row workloads about 10 %.
+template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL>
+__device__ __forceinline__ void spmm_short_rows(const SpmmArgs& a, int n_hub, int n_medium, int n_short) {
+  constexpr int U = U_REQUESTED < G ? U_REQUESTED : G;
+  constexpr int EPI = 32 / G;
+  constexpr int FT = VW * G * NV;
+  constexpr int BU = EPI * U;
+  const int lane = threadIdx.x & 31;
+  const int l = lane % G;
+  const int sub = lane / G;
+  const int f = a.f;
+  const uint64_t pol_keep = policy_evict_last();
+  const uint64_t pol_stream = policy_evict_first();
+  if (n_short > 0) {
+    const int* shorts = a.order + n_hub + n_medium;
+    const int n_batches = (n_short + 31) / 32;
+    const long long total = static_cast<long long>(n_batches) * a.n_tiles;
+    for (;;) {
+      const unsigned long long it = warp_next(&a.header->counter[2]);
+      if (it >= static_cast<unsigned long long>(total)) break;
+      const int tile = static_cast<int>(it / n_batches);
+      const int first = static_cast<int>(it - static_cast<unsigned long long>(tile) * n_batches) * 32;
+      const int n_here = n_short - first < 32 ? n_short - first : 32;
+      const int fbase = tile * FT;
+      int row_l = 0;
+      long long s_l = 0, e_l = 0;
+      if (lane < n_here) {
+        row_l = shorts[first + lane];
+        s_l = a.crow[row_l];
+        e_l = a.crow[row_l + 1];
+      }
+      bool fvalid[NV];
+      int foff[NV];
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        foff[v] = fbase + VW * (l + G * v);
+        fvalid[v] = foff[v] < f;
+      }
+      // columns / weights of row 0 of the batch
+      long long s_cur = __shfl_sync(kFull, s_l, 0);
+      int cnt_cur = static_cast<int>(__shfl_sync(kFull, e_l, 0) - s_cur);
+      int c_next = 0;
+      float w_next = 0.f;
+      if (lane < cnt_cur) {
+        c_next = static_cast<int>(ld_index(a.col + s_cur + lane, pol_stream));
+        if (HAS_VAL) w_next = ld_weight(a.val + s_cur + lane, pol_stream);
+      }
+      for (int r = 0; r < n_here; ++r) {
+        const int row = __shfl_sync(kFull, row_l, r);
+        const int cnt = cnt_cur;
+        const int c_l = c_next;
+        const float w_l = w_next;
+        if (r + 1 < n_here) {  // next row's columns while this row's X rows are gathered
+          s_cur = __shfl_sync(kFull, s_l, r + 1);
+          cnt_cur = static_cast<int>(__shfl_sync(kFull, e_l, r + 1) - s_cur);
+          if (lane < cnt_cur) {
+            c_next = static_cast<int>(ld_index(a.col + s_cur + lane, pol_stream));
+            if (HAS_VAL) w_next = ld_weight(a.val + s_cur + lane, pol_stream);
+          }
+        }
+        if (cnt == 0 && a.accumulate) continue;  // y += 0
+        float acc[NV][VW];
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
+        for (int j = 0; j < cnt; j += BU) {
+          float xv[U][NV][VW];
+          float wu[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int src = j + u * EPI + sub;
+            const int c = __shfl_sync(kFull, c_l, src);
+            if (HAS_VAL) wu[u] = __shfl_sync(kFull, w_l, src);
+            const bool ok = src < cnt;
+            if (!HAS_VAL) wu[u] = ok ? 1.f : 0.f;
+            if (HAS_VAL && !ok) wu[u] = 0.f;
+            const float* xrow = a.x + static_cast<long long>(c) * f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+              if (ok && fvalid[v]) {
+                VecIO<VW>::load(xv[u][v], xrow + foff[v], pol_keep);
+              } else {
+#pragma unroll
+                for (int i = 0; i < VW; ++i) xv[u][v][i] = 0.f;
+              }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+              for (int i = 0; i < VW; ++i) acc[v][i] = fmaf(wu[u], xv[u][v][i], acc[v][i]);
+        }
+#pragma unroll
+        for (int o = G; o < 32; o <<= 1)
+#pragma unroll
+          for (int v = 0; v < NV; ++v)
+#pragma unroll
+            for (int i = 0; i < VW; ++i) acc[v][i] += __shfl_xor_sync(kFull, acc[v][i], o);
+        if (sub == 0) {
+#pragma unroll
+          for (int v = 0; v < NV; ++v) {
+            if (fvalid[v]) {
+              float* dst = a.y + static_cast<size_t>(row) * f + foff[v];
+              if (a.accumulate) {
+                float old[VW];
+                VecIO<VW>::load_plain(old, dst);
+#pragma unroll
+                for (int i = 0; i < VW; ++i) acc[v][i] += old[i];
+              }
+              VecIO<VW>::store(dst, acc[v]);
+            }
+          }
+        }
+      }
+    }
+  }
+}
 
 template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL>
 __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
@@ -253,14 +382,16 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
   }
 
   // ------------------------------------------------------------------ queue 1: light rows
-  if (n_light > 0) {
-    const long long total = static_cast<long long>(n_light) * a.n_tiles;
+  const int n_short = a.header->n_short;
+  const int n_medium = n_light - n_short;  // light rows of 32 edges or more: one (row, tile) per grab
+  if (n_medium > 0) {
+    const long long total = static_cast<long long>(n_medium) * a.n_tiles;
     const int* light = a.order + n_hub;
     for (;;) {
       const unsigned long long it = warp_next(&a.header->counter[1]);
       if (it >= static_cast<unsigned long long>(total)) break;
-      const int tile = static_cast<int>(it / n_light);
-      const int row = light[it - static_cast<unsigned long long>(tile) * n_light];
+      const int tile = static_cast<int>(it / n_medium);
+      const int row = light[it - static_cast<unsigned long long>(tile) * n_medium];
       const int fbase = tile * FT;
       const long long s = a.crow[row];
       const long long e = a.crow[row + 1];
@@ -372,6 +503,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
       }
     }
   }
+
 }
 
 // Two entry kernels over the same body.  They differ only in the register budget the compiler is
@@ -385,6 +517,13 @@ __global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
 template <int VW, int G, int NV, int U, bool HAS_VAL>
 __global__ void __launch_bounds__(512, 1) spmm_kernel_deep(const SpmmArgs a) {
   spmm_body<VW, G, NV, U, HAS_VAL>(a);
+}
+
+template <int VW, int G, int NV, int U, bool HAS_VAL>
+__global__ void __launch_bounds__(512) spmm_short_kernel(const SpmmArgs a) {
+  const int n_hub = a.header->n_hub;
+  const int n_short = a.header->n_short;
+  if (n_short > 0) spmm_short_rows<VW, G, NV, U, HAS_VAL>(a, n_hub, a.header->n_light - n_short, n_short);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -407,6 +546,13 @@ static int launch_instance(const SpmmArgs& args, int warps, cudaStream_t stream,
   if (per_sm < 1) per_sm = 1;
   const int grid = sm_count(device) * per_sm;
   kernel<<<grid, threads, smem, stream>>>(args);
+  ASG_CUDA(cudaGetLastError());
+  // queue 2 (rows of fewer than 32 edges); leaves at once when the plan has none
+  auto short_kernel = spmm_short_kernel<VW, G, NV, U, HAS_VAL>;
+  int short_per_sm = 0;
+  ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&short_per_sm, short_kernel, threads, 0));
+  if (short_per_sm < 1) short_per_sm = 1;
+  short_kernel<<<sm_count(device) * short_per_sm, threads, 0, stream>>>(args);
   ASG_CUDA(cudaGetLastError());
   return ASG_OK;
 }

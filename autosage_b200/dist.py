@@ -3,20 +3,24 @@
 The reference is single-GPU.  For graphs that should be spread over 2/4/8 B200s the destination
 rows are cut into contiguous ranges balanced by nnz; rank r owns rows [b_r, b_{r+1}), the matching
 slice of col/val (row pointers rebased to 0), the X rows of the same range and the output rows.
-Every output row needs X rows of arbitrary columns, so X is all-gathered over NVLink: P-1 exchange
-steps on a communication stream, step s moving rank r's shard to rank (r - s) mod P while the
-shard of rank (r + s) mod P arrives.  To overlap, the local CSR is pre-split by column owner into
-P column blocks; the block of the rank's own columns is multiplied first (no wait) and each remote
-block as soon as its shard has landed, accumulating into the same output rows.  Summation order
-therefore differs from the single-GPU kernel (block by block) but stays inside the float32
-tolerance; all integer outputs (bounds, block CSRs) are deterministic.
+Every output row needs X rows of arbitrary columns, so X is gathered over NVLink into a full-height
+local buffer.  On CUDA the buffer lives in symmetric memory and each rank pulls the other P-1 shards
+with plain device-to-device copies on a side stream (copy engines, no SMs), in the order rank+1,
+rank+2, ...; with NCCL (or gloo on CPU) the same transfer is P-1 grouped send/recv steps, step s
+moving rank r's shard to rank (r - s) mod P while the shard of rank (r + s) mod P arrives.  To overlap,
+the local CSR is pre-split into column blocks by owner (optionally several consecutive arrivals per
+block); the block of the rank's own columns is multiplied first (no wait) and each further block as
+soon as its last shard has landed, accumulating into the same output rows.  Summation order therefore
+differs from the single-GPU kernel (block by block) but stays inside the float32 tolerance; all
+integer outputs (bounds, block CSRs) are deterministic.
 
-Remote data is always landed in local memory by the collective before a kernel reads it; ordering is
-by stream events only (no device-side waiting).  CPU tensors with the gloo backend run the same
+Remote data is always landed in local memory before a kernel reads it; ordering is by stream events
+and the symmetric-memory barriers only.  CPU tensors with the gloo backend run the same
 orchestration with torch's CPU SpMM, which is how the logic is tested without GPUs.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Optional
 
@@ -62,7 +66,8 @@ class RowShard:
     crow: torch.Tensor            # local row pointers, rebased to 0
     col: torch.Tensor             # global column ids
     val: Optional[torch.Tensor]
-    blocks: list[ColumnBlock] = field(default_factory=list)
+    blocks: list[ColumnBlock] = field(default_factory=list)   # one per column group, in arrival order
+    groups: list[list[int]] = field(default_factory=list)     # owners of each block
 
     @property
     def row_begin(self) -> int:
@@ -81,37 +86,66 @@ class RowShard:
         return int(self.bounds[-1])
 
 
+def arrival_order(rank: int, world: int) -> list[int]:
+    """Owners in the order their X shards become available on ``rank``: its own, then rank+1, ..."""
+    return [(rank + s) % world for s in range(world)]
+
+
+def column_groups(rank: int, world: int, groups: Optional[int] = None) -> list[list[int]]:
+    """The arrival order cut into ``groups`` runs of consecutive arrivals (all of them when None).
+    The SpMM of a group can start once its last member has arrived."""
+    order = arrival_order(rank, world)
+    k = world if groups is None else max(1, min(int(groups), world))
+    base, extra = divmod(world, k)
+    out, start = [], 0
+    for g in range(k):
+        size = base + (1 if g < extra else 0)
+        out.append(order[start:start + size])
+        start += size
+    return out
+
+
 def split_columns_by_owner(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor],
-                           bounds: torch.Tensor) -> list[ColumnBlock]:
-    """Stable partition of a CSR's edges by owner(col) = k with bounds[k] <= col < bounds[k+1]; edge
-    order inside a (row, owner) pair is preserved."""
+                           bounds: torch.Tensor, groups: Optional[list[list[int]]] = None) -> list[ColumnBlock]:
+    """Stable partition of a CSR's edges by the group of owner(col), owner k holding columns
+    bounds[k] <= col < bounds[k+1]; edge order inside a (row, group) pair is preserved.  Without
+    ``groups`` every owner is its own group, in owner order.  Block g covers groups[g]; its
+    ``owner`` field is the LAST owner of the group (the one whose arrival releases the block)."""
     world = bounds.numel() - 1
+    if groups is None:
+        groups = [[k] for k in range(world)]
     n_local = crow.numel() - 1
     device = col.device
     cuts = bounds[1:-1].to(device)
     owner = torch.bucketize(col, cuts, right=True) if world > 1 else torch.zeros_like(col)
+    group_of = torch.empty(world, dtype=torch.long)
+    for g, members in enumerate(groups):
+        for k in members:
+            group_of[k] = g
+    group = group_of.to(device)[owner]
     degrees = crow[1:] - crow[:-1]
     rows = torch.repeat_interleave(torch.arange(n_local, device=device, dtype=torch.long), degrees)
-    order = torch.argsort(owner * max(n_local, 1) + rows, stable=True)
-    owner_sorted = owner[order]
-    per_owner = torch.bincount(owner_sorted, minlength=world).cpu().tolist()
+    order = torch.argsort(group * max(n_local, 1) + rows, stable=True)
+    per_group = torch.bincount(group[order], minlength=len(groups)).cpu().tolist()
     blocks: list[ColumnBlock] = []
     start = 0
-    for k in range(world):
-        stop = start + per_owner[k]
+    for g, members in enumerate(groups):
+        stop = start + per_group[g]
         picked = order[start:stop]
         counts = torch.bincount(rows[picked], minlength=n_local)
         block_crow = torch.zeros(n_local + 1, dtype=torch.long, device=device)
         torch.cumsum(counts, 0, out=block_crow[1:])
-        blocks.append(ColumnBlock(k, block_crow, col[picked].contiguous(),
+        blocks.append(ColumnBlock(members[-1], block_crow, col[picked].contiguous(),
                                   None if val is None else val[picked].contiguous()))
         start = stop
     return blocks
 
 
 def shard_csr(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor], rank: int, world: int,
-              bounds: Optional[torch.Tensor] = None, device: Optional[torch.device] = None) -> RowShard:
-    """Cut rank ``rank``'s rows out of a full CSR (on any device) and build its column blocks."""
+              bounds: Optional[torch.Tensor] = None, device: Optional[torch.device] = None,
+              groups: Optional[int] = None) -> RowShard:
+    """Cut rank ``rank``'s rows out of a full CSR (on any device) and build its column blocks, one per
+    group of ``column_groups(rank, world, groups)`` in arrival order."""
     bounds = partition_rows(crow, world) if bounds is None else bounds
     lo, hi = int(bounds[rank]), int(bounds[rank + 1])
     first, last = int(crow[lo]), int(crow[hi])
@@ -124,7 +158,8 @@ def shard_csr(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor]
     local_crow, local_col = local_crow.contiguous(), local_col.contiguous()
     local_val = None if local_val is None else local_val.contiguous()
     shard = RowShard(rank, world, bounds, local_crow, local_col, local_val)
-    shard.blocks = split_columns_by_owner(local_crow, local_col, local_val, bounds)
+    shard.groups = column_groups(rank, world, groups)
+    shard.blocks = split_columns_by_owner(local_crow, local_col, local_val, bounds, shard.groups)
     return shard
 
 
@@ -155,10 +190,20 @@ def _block_spmm(block: ColumnBlock, x_full: torch.Tensor, y: torch.Tensor, accum
 
 
 class ShardedSpmm:
-    """Holds the gathered-X buffer, the communication stream and the per-block plans of one shard."""
+    """Holds the gathered-X buffer, the exchange machinery and the per-block plans of one shard.
+
+    Exchange modes
+      "peer"  (default on CUDA) X lives in symmetric memory (torch.distributed._symmetric_memory);
+              every rank PULLS the other shards with plain device-to-device copies on a side
+              stream, which the driver runs on the copy engines: NVLink traffic without occupying
+              SMs, so the column-block SpMMs keep the whole GPU.  One barrier before the pulls (all
+              shards written) and one after (all pulls done, shards may be overwritten).
+      "nccl"  P-1 grouped isend/irecv steps; also the path of the CPU/gloo tests.
+    """
 
     def __init__(self, shard: RowShard, features: int, *, group=None, dtype=torch.float32, feature_tile: int = 128,
-                 warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD) -> None:
+                 warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
+                 exchange: Optional[str] = None) -> None:
         self.shard = shard
         self.group = group
         self.features = features
@@ -167,8 +212,41 @@ class ShardedSpmm:
         self.device = device
         if device.type == "cuda" and not load_native():
             raise RuntimeError("libautosage_b200.so is required for the CUDA path")
-        self.x_full = torch.empty(shard.n_global, features, dtype=dtype, device=device)
         self.comm_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        self.handle = None
+        self.x_full = None
+        wanted = exchange or os.getenv("AUTOSAGE_EXCHANGE", "peer" if device.type == "cuda" else "nccl")
+        if wanted == "peer" and device.type == "cuda" and shard.world > 1:
+            self._try_symmetric(dtype)
+        if self.x_full is None:
+            self.x_full = torch.empty(shard.n_global, features, dtype=dtype, device=device)
+        self.exchange = "peer" if self.handle is not None else "nccl"
+        if not shard.groups:
+            shard.groups = [[k] for k in arrival_order(shard.rank, shard.world)]
+        self._events = [torch.cuda.Event() for _ in range(shard.world)] if device.type == "cuda" else []
+
+    def _try_symmetric(self, dtype) -> None:
+        """Allocate X in symmetric memory and map the peers' copies; all ranks agree on the outcome."""
+        ok = 1
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            pg = self.group if self.group is not None else dist.group.WORLD
+            buffer = symm.empty((self.shard.n_global, self.features), dtype=dtype, device=self.device)
+            handle = symm.rendezvous(buffer, pg)
+            peers = {}
+            b = self.shard.bounds
+            for owner in range(self.shard.world):
+                if owner != self.shard.rank:
+                    rows = int(b[owner + 1]) - int(b[owner])
+                    peers[owner] = handle.get_buffer(owner, (rows, self.features), dtype, int(b[owner]) * self.features)
+        except Exception as exc:  # noqa: BLE001 - any failure means "use NCCL send/recv instead"
+            self._symmetric_error = exc
+            ok = 0
+        flag = torch.tensor([ok], device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 1:
+            self.x_full, self.handle, self._peers = buffer, handle, peers
 
     @property
     def x_local(self) -> torch.Tensor:
@@ -180,6 +258,7 @@ class ShardedSpmm:
         return self.x_full[int(b[owner]):int(b[owner + 1])]
 
     def _start_exchange(self) -> list[tuple[int, list]]:
+        """NCCL/gloo mode: one grouped send+recv per step; returns (source rank, works) per step."""
         shard = self.shard
         steps: list[tuple[int, list]] = []
         for send_to, recv_from in exchange_schedule(shard.rank, shard.world):
@@ -187,6 +266,31 @@ class ShardedSpmm:
                    dist.P2POp(dist.irecv, self._shard_view(recv_from), recv_from, group=self.group)]
             steps.append((recv_from, dist.batch_isend_irecv(ops)))
         return steps
+
+    def _start_pulls(self) -> None:
+        """Peer mode, on the communication stream: barrier, one copy-engine pull per source in
+        arrival order (an event after each), barrier."""
+        shard = self.shard
+        self.handle.barrier(channel=0)
+        for owner in arrival_order(shard.rank, shard.world)[1:]:
+            self._shard_view(owner).copy_(self._peers[owner], non_blocking=True)
+            self._events[owner].record(self.comm_stream)
+        self.handle.barrier(channel=1)
+
+    def exchange_only(self) -> None:
+        """Runs just the gather of X (for measurements); the current stream waits for its end."""
+        if self.shard.world == 1:
+            return
+        if self.exchange == "peer":
+            current = torch.cuda.current_stream(self.device)
+            self.comm_stream.wait_stream(current)
+            with torch.cuda.stream(self.comm_stream):
+                self._start_pulls()
+            current.wait_stream(self.comm_stream)
+            return
+        for _, works in self._start_exchange():
+            for work in works:
+                work.wait()
 
     def forward(self, out: Optional[torch.Tensor] = None, overlap: bool = True) -> torch.Tensor:
         """y_local = A_local @ gather(X).  ``x_local`` must already hold this rank's features."""
@@ -197,6 +301,23 @@ class ShardedSpmm:
         if shard.world == 1:
             _block_spmm(shard.blocks[0], self.x_full, y, False, **kw)
             return y
+
+        if self.exchange == "peer":
+            current = torch.cuda.current_stream(self.device)
+            self.comm_stream.wait_stream(current)
+            with torch.cuda.stream(self.comm_stream):
+                self._start_pulls()
+            if not overlap:
+                current.wait_stream(self.comm_stream)
+            for g, (block, members) in enumerate(zip(shard.blocks, shard.groups)):
+                last = members[-1]
+                if overlap and last != shard.rank:
+                    current.wait_event(self._events[last])
+                _block_spmm(block, self.x_full, y, g > 0, **kw)
+            # the closing barrier of the exchange must be part of this step's stream order
+            current.wait_stream(self.comm_stream)
+            return y
+
         if self.comm_stream is not None:
             current = torch.cuda.current_stream(self.device)
             self.comm_stream.wait_stream(current)
@@ -204,16 +325,19 @@ class ShardedSpmm:
                 steps = self._start_exchange()
         else:
             steps = self._start_exchange()
-        if not overlap:
-            for _, works in steps:
-                for work in works:
-                    work.wait()
-        _block_spmm(shard.blocks[shard.rank], self.x_full, y, False, **kw)
-        for owner, works in steps:
-            if overlap:
+        arrived = {shard.rank}
+        pending = list(steps)
+        for g, (block, members) in enumerate(zip(shard.blocks, shard.groups)):
+            need = set(members) if overlap else set(range(shard.world))
+            while not need <= arrived:
+                source, works = pending.pop(0)
                 for work in works:
                     work.wait()  # CUDA: the current stream waits for the collective, the host does not
-            _block_spmm(shard.blocks[owner], self.x_full, y, True, **kw)
+                arrived.add(source)
+            _block_spmm(block, self.x_full, y, g > 0, **kw)
+        for _, works in pending:
+            for work in works:
+                work.wait()
         return y
 
 
@@ -221,11 +345,12 @@ class ShardedAutoSAGEConv(torch.nn.Module):
     """AutoSAGEConv over a row shard: gathered aggregation, then the layer's Linear on local rows."""
 
     def __init__(self, shard: RowShard, in_channels: int, out_channels: int, *, bias: bool = True, group=None,
-                 feature_tile: int = 128, warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD) -> None:
+                 feature_tile: int = 128, warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
+                 exchange: Optional[str] = None) -> None:
         super().__init__()
         self.linear = torch.nn.Linear(in_channels, out_channels, bias=bias)
         self.spmm = ShardedSpmm(shard, in_channels, group=group, feature_tile=feature_tile, warps=warps,
-                                threshold=threshold)
+                                threshold=threshold, exchange=exchange)
 
     def forward(self, x_local: Optional[torch.Tensor] = None, overlap: bool = True) -> torch.Tensor:
         if x_local is not None and x_local.data_ptr() != self.spmm.x_local.data_ptr():

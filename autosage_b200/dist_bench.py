@@ -55,7 +55,7 @@ def run(args):
     crow, col, info = syn.powerlaw_csr(spec, seed=0, device=device)
     n, nnz = info["rows"], info["nnz"]
     bounds = asg_dist.partition_rows(crow, world)
-    shard = asg_dist.shard_csr(crow, col, None, rank, world, bounds)
+    shard = asg_dist.shard_csr(crow, col, None, rank, world, bounds, groups=args.groups)
 
     # The same layer on ONE GPU (no sharding, no exchange), timed inside this job so that every
     # multi-GPU line carries its own strong-scaling reference.  Every rank times it on its own GPU
@@ -85,7 +85,7 @@ def run(args):
 
     torch.manual_seed(0)
     layer = asg_dist.ShardedAutoSAGEConv(shard, f, out_f, bias=True, feature_tile=args.tile, warps=args.warps,
-                                         threshold=args.hub_threshold).to(device)
+                                         threshold=args.hub_threshold, exchange=args.exchange).to(device)
     torch.nn.init.xavier_uniform_(layer.linear.weight)
     torch.nn.init.zeros_(layer.linear.bias)
     gen = torch.Generator(device=device).manual_seed(3)
@@ -134,22 +134,12 @@ def run(args):
         return float(reduce_max(torch.tensor([a.elapsed_time(b) / reps], device=device)).item())
 
     def exchange_only():
-        if not multi:
-            return
-        layer.spmm.comm_stream.wait_stream(stream)
-        with torch.cuda.stream(layer.spmm.comm_stream):
-            steps = layer.spmm._start_exchange()
-        for _, works in steps:
-            for work in works:
-                work.wait()
+        layer.spmm.exchange_only()
 
     def compute_only():
         kw = dict(feature_tile=args.tile, warps=args.warps, threshold=args.hub_threshold)
-        y = aggregated_scratch
-        asg_dist._block_spmm(shard.blocks[shard.rank], layer.spmm.x_full, y, False, **kw)
-        for k in range(world):
-            if k != shard.rank:
-                asg_dist._block_spmm(shard.blocks[k], layer.spmm.x_full, y, True, **kw)
+        for g, block in enumerate(shard.blocks):
+            asg_dist._block_spmm(block, layer.spmm.x_full, aggregated_scratch, g > 0, **kw)
 
     aggregated_scratch = torch.empty(shard.n_local, f, device=device)
     with torch.no_grad():
@@ -209,8 +199,10 @@ def run(args):
             "config": {
                 "workload": f"c5_conv: row-partitioned AutoSAGEConv forward, power-law CSR {n} rows, {nnz} nnz, "
                             f"F={f}, Linear {f}->{out_f}, unweighted",
-                "parallelism": f"rows sharded by nnz over {world} GPUs; X all-gathered over NCCL in {world - 1} "
-                               f"send/recv steps overlapped with column-block SpMM",
+                "parallelism": f"rows sharded by nnz over {world} GPUs; X gathered over NVLink "
+                               f"({'copy-engine pulls from peer memory' if layer.spmm.exchange == 'peer' else 'NCCL send/recv steps'}), "
+                               f"overlapped with {len(shard.blocks)} column-block SpMMs per GPU",
+                "exchange": layer.spmm.exchange,
                 "kernel_parameters": {"feature_tile": args.tile, "warps_per_block": args.warps,
                                       "hub_threshold": args.hub_threshold},
                 "l2": "per-GPU inputs per step (CSR shard + gathered X) exceed the 126 MB L2; no explicit flush",
@@ -240,7 +232,8 @@ def run(args):
                 "d2h_bytes_per_step": int(io_bytes[1].item()),
                 "steps": e2e_steps,
             },
-            "gpu_launches": args.steps * world * world,
+            # per step and GPU: two SpMM kernels (main + short-row queue) for every column block
+            "gpu_launches": args.steps * world * len(shard.blocks) * 2,
             "clocks": clocks.summary(),
         }
     if multi:

@@ -335,7 +335,8 @@ def run_ours_single(args) -> dict:
             "d2h_bytes_per_step": d2h_bytes,
             "steps": e2e_steps,
         },
-        "gpu_launches": args.steps,
+        # SpMM and attention launch two kernels per step (main queues + the short-row queue)
+        "gpu_launches": args.steps * (1 if args.workload == "c3_sddmm" else 2),
         "clocks": clocks.summary(),
     }
 
@@ -432,6 +433,8 @@ def main() -> None:
     parser.add_argument("--hub-threshold", type=int, default=1024)
     parser.add_argument("--cpu-sample-nnz", type=int, default=4_000_000)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--groups", type=int, default=None, help="column groups per GPU in the sharded path")
+    parser.add_argument("--exchange", default=None, choices=["peer", "nccl"], help="how X is gathered (sharded path)")
     args = parser.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

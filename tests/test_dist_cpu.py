@@ -62,13 +62,38 @@ def test_exchange_schedule_is_a_perfect_matching_every_step():
             assert sorted(src for _, src in asg_dist.exchange_schedule(r, world)) == [k for k in range(world) if k != r]
 
 
+def test_column_groups_follow_arrival_order():
+    assert asg_dist.arrival_order(2, 4) == [2, 3, 0, 1]
+    assert asg_dist.column_groups(2, 4) == [[2], [3], [0], [1]]
+    assert asg_dist.column_groups(2, 4, 2) == [[2, 3], [0, 1]]
+    assert asg_dist.column_groups(0, 8, 3) == [[0, 1, 2], [3, 4, 5], [6, 7]]
+    assert asg_dist.column_groups(5, 8, 100) == [[k % 8] for k in range(5, 13)]
+    assert asg_dist.column_groups(1, 3, 1) == [[1, 2, 0]]
+    # grouped blocks still reassemble the shard and only hold their owners' columns
+    crow, col = random_csr(240, 9, seed=4)
+    val = weights(col.numel(), 2)
+    x = dense(240, 8, 3)
+    bounds = asg_dist.partition_rows(crow, 4)
+    for groups in (1, 2, 3, 4):
+        shard = asg_dist.shard_csr(crow, col, val, 1, 4, bounds, groups=groups)
+        assert len(shard.blocks) == groups and shard.groups == asg_dist.column_groups(1, 4, groups)
+        acc = np.zeros((shard.n_local, 8))
+        for block, members in zip(shard.blocks, shard.groups):
+            assert block.owner == members[-1]
+            owners = torch.bucketize(block.col, bounds[1:-1], right=True)
+            assert set(owners.tolist()) <= set(members)
+            acc += orc.spmm(to_np(block.crow), to_np(block.col), to_np(block.val), to_np(x))
+        exact = orc.spmm(to_np(shard.crow), to_np(shard.col), to_np(shard.val), to_np(x))
+        np.testing.assert_allclose(acc, exact, rtol=1e-12, atol=1e-12)
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, overlap: bool, out_dir: str):
+def _worker(rank: int, world: int, port: int, overlap: bool, out_dir: str, groups=None):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -77,9 +102,10 @@ def _worker(rank: int, world: int, port: int, overlap: bool, out_dir: str):
         val = weights(col.numel(), 4)
         x = dense(400, 24, 5)
         bounds = asg_dist.partition_rows(crow, world)
-        shard = asg_dist.shard_csr(crow, col, val, rank, world, bounds)
+        shard = asg_dist.shard_csr(crow, col, val, rank, world, bounds, groups=groups)
         torch.manual_seed(0)
         layer = asg_dist.ShardedAutoSAGEConv(shard, 24, 8)
+        assert layer.spmm.exchange == "nccl"  # CPU ranks use grouped send/recv
         layer.spmm.x_full.fill_(float("nan"))  # anything not received stays NaN and poisons the result
         with torch.no_grad():
             out = layer(x[shard.row_begin:shard.row_end], overlap=overlap)
@@ -92,9 +118,9 @@ def _worker(rank: int, world: int, port: int, overlap: bool, out_dir: str):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,overlap", [(2, True), (2, False), (3, True)])
-def test_sharded_conv_on_gloo_ranks(tmp_path, world, overlap):
-    mp.spawn(_worker, args=(world, _free_port(), overlap, str(tmp_path)), nprocs=world, join=True)
+@pytest.mark.parametrize("world,overlap,groups", [(2, True, None), (2, False, None), (3, True, None), (3, True, 2)])
+def test_sharded_conv_on_gloo_ranks(tmp_path, world, overlap, groups):
+    mp.spawn(_worker, args=(world, _free_port(), overlap, str(tmp_path), groups), nprocs=world, join=True)
     crow, col = random_csr(400, 9, seed=21, hubs={7: 900, 350: 300})
     val = weights(col.numel(), 4)
     x = dense(400, 24, 5)
