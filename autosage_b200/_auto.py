@@ -37,6 +37,7 @@ _INF = float("inf")
 # ------------------------------------------------------------------------------------------------
 # timing
 # ------------------------------------------------------------------------------------------------
+@torch.no_grad()  # probes never need an autograd graph
 def _time_cuda(function: Callable[[], torch.Tensor], *, warmup: int, iterations: int,
                cap_ms: Optional[float] = None) -> dict[str, Any]:
     """CUDA-event timing of ``function``: ``warmup`` untimed calls, then up to ``iterations`` timed
@@ -220,7 +221,10 @@ def _replay_miss(operation: str, baseline_name: str) -> dict[str, Any]:
 
 
 def _run_spmm_choice(choice, candidate, crow, col, val, x) -> torch.Tensor:
-    if choice == "autosage":
+    # torch's CSR SpMM cannot differentiate with respect to the values of a pattern that repeats a
+    # column inside a row; a "baseline" schedule then runs the native operator, which can.
+    needs_value_grad = val is not None and val.requires_grad and torch.is_grad_enabled()
+    if choice == "autosage" or (needs_value_grad and x.is_cuda and native_op("spmm_csr") is not None):
         split, core = native_op("spmm_csr_split"), native_op("spmm_csr")
         if split is not None and candidate is not None:
             return split(crow, col, val, x, *(int(c) for c in candidate))
@@ -541,7 +545,9 @@ def _csr_row_softmax(crow: torch.Tensor, scores: torch.Tensor) -> torch.Tensor:
     kernel; everything else runs the reference's scatter formulation (``_auto.py:744-759``)."""
     if scores.numel() == 0:
         return scores.clone()
-    if scores.is_cuda and scores.dtype == torch.float32 and crow.dtype == torch.long and load_native():
+    differentiating = torch.is_grad_enabled() and scores.requires_grad  # the kernel has no backward
+    if (scores.is_cuda and scores.dtype == torch.float32 and crow.dtype == torch.long and not differentiating
+            and load_native()):
         crow = crow.contiguous()
         scores = scores.contiguous()
         probs = torch.empty_like(scores)
@@ -591,6 +597,8 @@ def csr_attention_forward(crow, col, query, key, value, *, guardrail: float = 0.
     three-pass composition.  The info dict keeps the reference's two keys and adds "attention".
     """
     use_fused = _fused_attention_enabled() if fused is None else bool(fused)
+    if torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad):
+        use_fused = False  # the fused kernel is forward-only; the three-pass composition is differentiable
     eligible = (query.is_cuda and query.dtype == torch.float32 and key.dtype == torch.float32
                 and value.dtype == torch.float32 and query.ndim == 2 and query.shape == key.shape == value.shape
                 and query.size(1) <= 512)

@@ -234,7 +234,8 @@ int asg_sddmm_csr_split(const int64_t* crow, const int64_t* col, const float* q,
 
 int asg_sddmm_csr(const int64_t* crow, const int64_t* col, const float* q, const float* k, float* out,
                   int64_t n_rows, int64_t nnz, int64_t f, void* workspace, size_t workspace_bytes, void* stream) {
-  return asg::sddmm_entry(crow, col, q, k, out, n_rows, nnz, f, 8, 2048, 0u, workspace, workspace_bytes, stream);
+  // SDDMM has no reduction across the edges of a row, so only very long rows gain from a whole CTA
+  return asg::sddmm_entry(crow, col, q, k, out, n_rows, nnz, f, 8, 8192, 0u, workspace, workspace_bytes, stream);
 }
 
 }  // extern "C"

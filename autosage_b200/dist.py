@@ -28,6 +28,7 @@ import torch
 import torch.distributed as dist
 
 from . import _native
+from .conv import apply_linear
 from .ops import DEFAULT_HUB_THRESHOLD, DEFAULT_WARPS, load_native
 
 
@@ -356,4 +357,4 @@ class ShardedAutoSAGEConv(torch.nn.Module):
         if x_local is not None and x_local.data_ptr() != self.spmm.x_local.data_ptr():
             self.spmm.x_local.copy_(x_local)
         aggregated = self.spmm.forward(overlap=overlap)
-        return self.linear(aggregated)
+        return apply_linear(self.linear, aggregated)

@@ -146,7 +146,7 @@ def run(args):
         breakdown = {
             "exchange_ms": round(timed(exchange_only), 4),
             "block_spmm_ms": round(timed(compute_only), 4),
-            "linear_ms": round(timed(lambda: layer.linear(aggregated_scratch)), 4),
+            "linear_ms": round(timed(lambda: asg_dist.apply_linear(layer.linear, aggregated_scratch)), 4),
         }
     del aggregated_scratch
 

@@ -16,8 +16,12 @@ import torch
 
 from . import _native
 
-DEFAULT_WARPS = 8
-DEFAULT_HUB_THRESHOLD = 2048
+# defaults of the plain operators, from the B200 sweeps (see the C entry points asg_spmm_csr / asg_sddmm_csr)
+DEFAULT_WARPS = 4
+DEFAULT_HUB_THRESHOLD = 1024
+DEFAULT_TILE = 64
+SDDMM_WARPS = 8
+SDDMM_HUB_THRESHOLD = 8192
 
 _ATTEMPTED = False
 _ERROR: Optional[BaseException] = None
@@ -76,9 +80,8 @@ def _op_spmm_csr(crow, col, val, x):
     y = torch.empty_like(x)
     if x.numel() == 0:
         return y
-    tile = 64 if x.size(1) <= 64 else 128
     workspace, ready = _native.planned_workspace(crow, DEFAULT_HUB_THRESHOLD)
-    _native.spmm(crow, col, val, x, y, feature_tile=tile, warps=DEFAULT_WARPS, threshold=DEFAULT_HUB_THRESHOLD,
+    _native.spmm(crow, col, val, x, y, feature_tile=DEFAULT_TILE, warps=DEFAULT_WARPS, threshold=DEFAULT_HUB_THRESHOLD,
                  flags=_base_flags() | ready, workspace=workspace)
     return y
 
@@ -102,8 +105,8 @@ def _op_sddmm_csr(crow, col, query, key):
     out = torch.empty(col.numel(), dtype=query.dtype, device=query.device)
     if query.size(0) == 0 or col.numel() == 0:
         return out
-    workspace, ready = _native.planned_workspace(crow, DEFAULT_HUB_THRESHOLD)
-    _native.sddmm(crow, col, query, key, out, warps=DEFAULT_WARPS, threshold=DEFAULT_HUB_THRESHOLD,
+    workspace, ready = _native.planned_workspace(crow, SDDMM_HUB_THRESHOLD)
+    _native.sddmm(crow, col, query, key, out, warps=SDDMM_WARPS, threshold=SDDMM_HUB_THRESHOLD,
                   flags=_base_flags() | ready, workspace=workspace)
     return out
 
@@ -133,11 +136,85 @@ _SCHEMAS = (
 )
 
 
+# ------------------------------------------------------------------------------------------------
+# Autograd.  The reference registers no backward for its operators (its CUDA path is forward-only);
+# here the four operators are differentiable in val / x and query / key, each gradient being one of
+# the same kernels:
+#   Y = A X          dX = A^T dY (SpMM over the transposed pattern),  dval[e] = <dY[row e], X[col e]> (SDDMM)
+#   s[e] = <Q_r,K_c> dQ = A(ds) K (SpMM with the edge gradients as weights),  dK = A(ds)^T Q
+# ------------------------------------------------------------------------------------------------
+_TRANSPOSES: dict[tuple, tuple] = {}
+
+
+def _transposed_pattern(crow: torch.Tensor, col: torch.Tensor):
+    """(crow_t, col_t, perm) of the transposed square pattern; perm[i] is the position in the original
+    edge order of the i-th edge of the transpose.  Memoised per (crow, col) tensor pair."""
+    import weakref
+
+    key = (crow.data_ptr(), col.data_ptr(), crow.numel(), col.numel())
+    hit = _TRANSPOSES.get(key)
+    if hit is not None and hit[0]() is crow and hit[1]() is col and hit[2] == (crow._version, col._version):
+        return hit[3]
+    n = crow.numel() - 1
+    rows = torch.repeat_interleave(torch.arange(n, device=col.device, dtype=torch.long), crow[1:] - crow[:-1])
+    perm = torch.argsort(col, stable=True)
+    crow_t = torch.zeros(n + 1, dtype=torch.long, device=col.device)
+    if col.numel():
+        torch.cumsum(torch.bincount(col, minlength=n)[:n], 0, out=crow_t[1:])
+    value = (crow_t, rows[perm].contiguous(), perm)
+    if len(_TRANSPOSES) > 16:
+        _TRANSPOSES.clear()
+    _TRANSPOSES[key] = (weakref.ref(crow), weakref.ref(col), (crow._version, col._version), value)
+    return value
+
+
+def _spmm_setup(ctx, inputs, output) -> None:
+    crow, col, val, x = inputs[:4]
+    ctx.extra = tuple(inputs[4:])  # (feature_tile, warps_per_block, hub_threshold) for the split operator
+    ctx.save_for_backward(crow, col, val, x)
+
+
+def _spmm_backward(ctx, grad_y):
+    crow, col, val, x = ctx.saved_tensors
+    grad_y = grad_y.contiguous()
+    run = (lambda c, k, v, d: torch.ops.autosage.spmm_csr_split(c, k, v, d, *ctx.extra)) if ctx.extra else \
+        torch.ops.autosage.spmm_csr
+    grad_x = grad_val = None
+    if ctx.needs_input_grad[3]:
+        crow_t, col_t, perm = _transposed_pattern(crow, col)
+        grad_x = run(crow_t, col_t, None if val is None else val.detach()[perm].contiguous(), grad_y)
+    if val is not None and ctx.needs_input_grad[2]:
+        grad_val = torch.ops.autosage.sddmm_csr(crow, col, grad_y, x.detach())
+    return (None, None, grad_val, grad_x) + (None,) * len(ctx.extra)
+
+
+def _sddmm_setup(ctx, inputs, output) -> None:
+    crow, col, query, key = inputs[:4]
+    ctx.save_for_backward(crow, col, query, key)
+
+
+def _sddmm_backward(ctx, grad_out):
+    crow, col, query, key = ctx.saved_tensors
+    grad_out = grad_out.contiguous()
+    grad_q = grad_k = None
+    if ctx.needs_input_grad[2]:
+        grad_q = torch.ops.autosage.spmm_csr(crow, col, grad_out, key.detach())
+    if ctx.needs_input_grad[3]:
+        crow_t, col_t, perm = _transposed_pattern(crow, col)
+        grad_k = torch.ops.autosage.spmm_csr(crow_t, col_t, grad_out[perm].contiguous(), query.detach())
+    return (None, None, grad_q, grad_k) + (None,) * (len(ctx.needs_input_grad) - 4)
+
+
 def _register_operators() -> None:
     definitions = torch.library.Library("autosage", "FRAGMENT")
     for name, schema, function in _SCHEMAS:
         definitions.define(name + schema)
         definitions.impl(name, function, "CUDA")
+    for name in ("spmm_csr", "spmm_csr_split"):
+        torch.library.register_autograd(f"autosage::{name}", _spmm_backward, setup_context=_spmm_setup, lib=definitions)
+    for name in ("sddmm_csr", "sddmm_csr_split"):
+        torch.library.register_autograd(f"autosage::{name}", _sddmm_backward, setup_context=_sddmm_setup,
+                                        lib=definitions)
     _LIBRARY_HANDLES.append(definitions)
 
 

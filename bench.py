@@ -6,8 +6,10 @@
 One "step" is one pass of the hot path (one SpMM / SDDMM / attention call) over the whole synthetic
 graph.  Metric: algorithmic GB/s (bytes = CSR + gathered dense rows + output, the byte model of the
 roofline) with edges*F/s alongside.  N = 1 runs BASELINE configuration 2 (232,965 rows, ~114.6 M
-nnz, weighted, F = 128); N > 1 shards the rows of configuration 5 (2,449,029 rows, ~123.7 M nnz)
-by nnz over the ranks, all-gathers X over NCCL inside the timed region and reports strong scaling.
+nnz, weighted, F = 128); N > 1 runs the row-partitioned AutoSAGEConv forward of configuration 5
+(2,449,029 rows, ~123.7 M nnz, Linear F->256): rows sharded by nnz over the ranks, X gathered over
+NVLink inside the timed region (peer-memory pulls, or NCCL send/recv with --exchange nccl), strong
+scaling; each such line also carries the same layer timed on one GPU (single_gpu_ms_per_step).
 
 The line printed by rank 0 carries, beside the contract keys:
   roofline      achieved algorithmic GB/s of the dominant kernel against the measured HBM copy peak
@@ -35,6 +37,13 @@ if str(ROOT) not in sys.path:
 import torch  # noqa: E402
 
 FALLBACK_HBM_GBS = 6650.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (key: workload, F, feature tile).  Workloads without a capture
+# of the byte counters report null.
+NCU_DRAM_TRAFFIC = {
+    ("c2_spmm", 128, 64): (6.04e9, "profiles/spmm_kernel_c2_f128.md"),
+}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -324,7 +333,10 @@ def run_ours_single(args) -> dict:
             "peak_source": f"{peak_kind} HBM copy bandwidth (burst)",
             "unit": "GB/s",
             "frac": round(achieved / peak, 4),
-            "traffic": None,
+            "traffic": NCU_DRAM_TRAFFIC.get((args.workload, f, tile), (None, None))[0],
+            "traffic_source": NCU_DRAM_TRAFFIC.get((args.workload, f, tile), (None, None))[1],
+            "note": "achieved counts every gathered dense row (CSR + gathered rows + output); when the dense operand "
+                    "fits the 126 MB L2 the gather is served by L2 and achieved exceeds the HBM peak",
             "launch_ms": round(launch_ms, 4),
         },
         "e2e": {

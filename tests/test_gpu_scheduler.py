@@ -212,3 +212,54 @@ def test_convolution_on_gpu_matches_the_cpu_layer(asg, isolated_cache):
         assert info["operation"] == "spmm"
         if mode == "native":
             assert info == {"operation": "spmm", "choice": "native", "from_cache": False}
+
+
+def test_operators_are_differentiable(asg, isolated_cache):
+    """Gradients of the operators against dense autograd (the reference registers no backward)."""
+    crow, col = random_csr(300, 7, seed=12, hubs={4: 900})
+    n = 300
+    val = weights(col.numel(), 3).cuda().requires_grad_()
+    x = dense(n, 48, 4).cuda().requires_grad_()
+    crow_d, col_d = crow.cuda(), col.cuda()
+    rows = torch.repeat_interleave(torch.arange(n, device="cuda"), crow_d[1:] - crow_d[:-1])
+
+    def dense_adj(v):
+        return torch.zeros(n, n, device="cuda").index_put((rows, col_d), v, accumulate=True)
+
+    upstream = dense(n, 48, 5).cuda()
+    for op in (lambda: torch.ops.autosage.spmm_csr(crow_d, col_d, val, x),
+               lambda: torch.ops.autosage.spmm_csr_split(crow_d, col_d, val, x, 64, 4, 64)):
+        val.grad = x.grad = None
+        (op() * upstream).sum().backward()
+        got_val, got_x = val.grad.clone(), x.grad.clone()
+        val.grad = x.grad = None
+        ((dense_adj(val) @ x) * upstream).sum().backward()
+        assert torch.allclose(got_x, x.grad, rtol=1e-4, atol=1e-3)
+        assert torch.allclose(got_val, val.grad, rtol=1e-4, atol=1e-3)
+    # unweighted: only x gets a gradient
+    x.grad = None
+    (torch.ops.autosage.spmm_csr(crow_d, col_d, None, x) * upstream).sum().backward()
+    ones = torch.ones(col.numel(), device="cuda")
+    assert torch.allclose(x.grad, dense_adj(ones).t() @ upstream, rtol=1e-4, atol=1e-3)
+
+    q = dense(n, 32, 6).cuda().requires_grad_()
+    k = dense(n, 32, 7).cuda().requires_grad_()
+    g = dense(col.numel(), 1, 8).flatten().cuda()
+    (torch.ops.autosage.sddmm_csr(crow_d, col_d, q, k) * g).sum().backward()
+    got_q, got_k = q.grad.clone(), k.grad.clone()
+    q.grad = k.grad = None
+    (((q[rows] * k[col_d]).sum(1)) * g).sum().backward()
+    assert torch.allclose(got_q, q.grad, rtol=1e-4, atol=1e-3)
+    assert torch.allclose(got_k, k.grad, rtol=1e-4, atol=1e-3)
+
+    # the layer trains: loss goes through AutoSAGEConv on the GPU, attention falls back to the
+    # differentiable three-pass composition when gradients are requested
+    layer = asg.AutoSAGEConv(48, 8, mode="native").cuda()
+    edge_index = torch.stack((col_d, rows))
+    layer(x, edge_index).square().mean().backward()
+    assert layer.linear.weight.grad is not None and torch.isfinite(layer.linear.weight.grad).all()
+    qq = dense(n, 32, 9).cuda().requires_grad_()
+    out, info = asg.csr_attention_forward(crow_d, col_d, qq, k.detach(), dense(n, 32, 10).cuda(), scale=0.2)
+    assert set(info) == {"sddmm", "spmm"}
+    out.sum().backward()
+    assert qq.grad is not None and torch.isfinite(qq.grad).all()
