@@ -1,9 +1,9 @@
 """Multi-GPU leg of bench.py: BASELINE configuration 5, the row-partitioned AutoSAGEConv forward.
 
 Launched by ``torch.distributed.run`` with one rank per GPU.  Every rank builds the same seeded
-graph on its own GPU, keeps its nnz-balanced row shard, and the timed step is: all-gather of X
-over NCCL (overlapped, shard by shard, with the column-block SpMMs) followed by the Linear F->256 on
-the local rows.  Time is the maximum over ranks of the CUDA-event time between two barriers; the
+graph on its own GPU, keeps its nnz-balanced row shard, and the timed step is: gather of X over
+NVLink (copy-engine pulls from peer memory, or NCCL send/recv; overlapped, shard by shard, with the
+column-block SpMMs) followed by the Linear F->256 on the local rows.  Time is the maximum over ranks of the CUDA-event time between two barriers; the
 reported value is whole-job algorithmic bytes (SpMM: CSR + gathered X + output; Linear: read
 aggregated rows + write outputs) divided by that time.  Strong scaling: total work is fixed.
 """
