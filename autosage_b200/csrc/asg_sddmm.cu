@@ -1,8 +1,9 @@
 // CSR SDDMM for sm_100a: out[e] = <Q[row(e), :], K[col[e], :]>.
 //
-// One persistent kernel, two work queues (see asg_plan.cu):
+// Persistent kernels over the work queues of the plan (see asg_plan.cu):
 //   queue 0  hub rows, one CTA each: the warps of the CTA take the row's 32-edge batches round-robin
-//   queue 1  light rows, one warp each
+//   queue 1  light rows of 32 edges or more, one warp each
+//   queue 2  light rows of fewer than 32 edges, 32 rows per grab (sddmm_short_kernel)
 // For a batch the warp loads 32 column indices with one coalesced load, keeps the Q row in
 // registers, gathers the K rows with vector loads (U instructions in flight per lane), and
 // turns the per-lane partial dot products into one finished value per lane with a
@@ -109,13 +110,91 @@ __global__ void ASG_BOUNDS sddmm_kernel(const SddmmArgs a) {
       sddmm_row_batches<VW, G, NV, U>(a, row, s + 32ll * warp, 32ll * n_warps, lane, pol_keep, pol_stream);
     }
   }
-  if (n_light > 0) {
+  const int n_short = a.header->n_short;
+  const int n_medium = n_light - n_short;  // light rows of 32 edges or more: one row per grab
+  if (n_medium > 0) {
     const int* light = a.order + n_hub;
     for (;;) {
       const unsigned long long it = warp_next(&a.header->counter[1]);
-      if (it >= static_cast<unsigned long long>(n_light)) break;
+      if (it >= static_cast<unsigned long long>(n_medium)) break;
       const int row = light[it];
       sddmm_row_batches<VW, G, NV, U>(a, row, a.crow[row], 32ll, lane, pol_keep, pol_stream);
+    }
+  }
+}
+
+// Queue 2 as a kernel of its own (launched right after the main one; inlined it raised the main
+// kernel from 78 to 120 registers).  Rows of fewer than 32 edges, 32 rows per grab: ids and row
+// pointers arrive with one coalesced load each and the next row's columns are fetched while the current
+// row's K rows are gathered.
+template <int VW, int G, int NV, int U>
+__global__ void __launch_bounds__(512) sddmm_short_kernel(const SddmmArgs a) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t pol_keep = policy_evict_last();
+  const uint64_t pol_stream = policy_evict_first();
+  const int n_hub = a.header->n_hub;
+  const int n_short = a.header->n_short;
+  const int n_medium = a.header->n_light - n_short;
+  if (n_short > 0) {
+    constexpr int EPI = 32 / G;
+    constexpr int FT = VW * G * NV;
+    const int l = lane % G;
+    const int sub = lane / G;
+    const int f = a.f;
+    const int* shorts = a.order + n_hub + n_medium;
+    const int n_batches = (n_short + 31) / 32;
+    for (;;) {
+      const unsigned long long it = warp_next(&a.header->counter[2]);
+      if (it >= static_cast<unsigned long long>(n_batches)) break;
+      const int first = static_cast<int>(it) * 32;
+      const int n_here = n_short - first < 32 ? n_short - first : 32;
+      int row_l = 0;
+      long long s_l = 0, e_l = 0;
+      if (lane < n_here) {
+        row_l = shorts[first + lane];
+        s_l = a.crow[row_l];
+        e_l = a.crow[row_l + 1];
+      }
+      long long s_cur = __shfl_sync(kFull, s_l, 0);
+      int cnt_cur = static_cast<int>(__shfl_sync(kFull, e_l, 0) - s_cur);
+      int c_next = 0;
+      if (lane < cnt_cur) c_next = static_cast<int>(ld_index(a.col + s_cur + lane, pol_stream));
+      for (int r = 0; r < n_here; ++r) {
+        const int row = __shfl_sync(kFull, row_l, r);
+        const long long s = s_cur;
+        const int cnt = cnt_cur;
+        const int c_l = c_next;
+        if (r + 1 < n_here) {
+          s_cur = __shfl_sync(kFull, s_l, r + 1);
+          cnt_cur = static_cast<int>(__shfl_sync(kFull, e_l, r + 1) - s_cur);
+          if (lane < cnt_cur) c_next = static_cast<int>(ld_index(a.col + s_cur + lane, pol_stream));
+        }
+        if (cnt == 0) continue;
+        const float* qrow = a.q + static_cast<size_t>(row) * f;
+        float part[G];
+#pragma unroll
+        for (int i = 0; i < G; ++i) part[i] = 0.f;
+        for (int tile = 0; tile < a.n_tiles; ++tile) {
+          float q[NV][VW];
+          bool fvalid[NV];
+          int foff[NV];
+#pragma unroll
+          for (int v = 0; v < NV; ++v) {
+            foff[v] = tile * FT + VW * (l + G * v);
+            fvalid[v] = foff[v] < f;
+            if (fvalid[v]) {
+              VecIO<VW>::load(q[v], qrow + foff[v], pol_stream);
+            } else {
+#pragma unroll
+              for (int i = 0; i < VW; ++i) q[v][i] = 0.f;
+            }
+          }
+          batch_dots<VW, G, NV, U, false>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
+        }
+        const float dot = group_reduce_scatter<G>(part, l);
+        const int edge = l * EPI + sub;
+        if (edge < cnt) st_stream1(a.out + s + edge, dot);
+      }
     }
   }
 }
@@ -128,6 +207,12 @@ static int launch_instance(const SddmmArgs& args, int warps, cudaStream_t stream
   ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
   if (per_sm < 1) per_sm = 1;
   kernel<<<sm_count(device) * per_sm, threads, 0, stream>>>(args);
+  ASG_CUDA(cudaGetLastError());
+  auto short_kernel = sddmm_short_kernel<VW, G, NV, U>;
+  int short_per_sm = 0;
+  ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&short_per_sm, short_kernel, threads, 0));
+  if (short_per_sm < 1) short_per_sm = 1;
+  short_kernel<<<sm_count(device) * short_per_sm, threads, 0, stream>>>(args);
   ASG_CUDA(cudaGetLastError());
   return ASG_OK;
 }

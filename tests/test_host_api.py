@@ -320,3 +320,29 @@ def test_cuda_request_without_a_device_fails_loudly(monkeypatch):
         torch.ops.autosage.spmm_csr(crow, col, None, torch.ones(2, 4))
     with pytest.raises(NotImplementedError):
         torch.ops.autosage.sddmm_csr_split(crow, col, torch.ones(2, 4), torch.ones(2, 4), 8, 16)
+
+
+def test_transposed_pattern_for_the_backward_pass():
+    from autosage_b200.ops import _transposed_pattern
+
+    crow, col = torch.tensor([0, 2, 2, 3, 6]), torch.tensor([1, 2, 0, 3, 1, 1])  # row 3 repeats column 1
+    crow_t, col_t, perm = _transposed_pattern(crow, col)
+    dense = torch.zeros(4, 4)
+    rows = torch.repeat_interleave(torch.arange(4), crow[1:] - crow[:-1])
+    dense.index_put_((rows, col), torch.ones(6), accumulate=True)
+    rows_t = torch.repeat_interleave(torch.arange(4), crow_t[1:] - crow_t[:-1])
+    dense_t = torch.zeros(4, 4).index_put_((rows_t, col_t), torch.ones(6), accumulate=True)
+    assert torch.equal(dense_t, dense.t())
+    assert torch.equal(col[perm], rows_t) and torch.equal(rows[perm], col_t)   # perm maps transpose edges back
+    assert _transposed_pattern(crow, col)[0] is crow_t                           # memoised per tensor pair
+    col[0] = 3                                                                   # in-place edit invalidates
+    assert _transposed_pattern(crow, col)[0] is not crow_t
+
+
+def test_linear_helper_matches_the_module_on_cpu():
+    from autosage_b200.conv import apply_linear
+
+    torch.manual_seed(0)
+    layer = torch.nn.Linear(5, 3)
+    x = torch.randn(7, 5)
+    assert torch.equal(apply_linear(layer, x), layer(x))
