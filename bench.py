@@ -301,6 +301,25 @@ def run_ours_single(args) -> dict:
     e2e_ms = e_begin.elapsed_time(e_end) / e2e_steps
     d2h_bytes = result_host.numel() * result_host.element_size()
 
+    # The same call with the graph kept on the device (as a model keeps its weights) and only the dense
+    # operands copied in every step - how a GNN layer is fed.  Reported beside e2e, not instead of it.
+    graph_dev = [t.to(device) for t in pinned[:2]]
+    dense_pinned = pinned[2:]
+
+    def e2e_dense_only():
+        dev_inputs = graph_dev + [t.to(device, non_blocking=True) for t in dense_pinned]
+        result_host.copy_(e2e_step(dev_inputs), non_blocking=True)
+
+    e2e_dense_only()
+    torch.cuda.synchronize()
+    e_begin.record(stream)
+    for _ in range(e2e_steps):
+        e2e_dense_only()
+    e_end.record(stream)
+    torch.cuda.synchronize()
+    e2e_dense_ms = e_begin.elapsed_time(e_end) / e2e_steps
+    dense_bytes = sum(t.numel() * t.element_size() for t in dense_pinned)
+
     line = {
         "metric": "algorithmic_GBps",
         "value": round(value, 2),
@@ -346,6 +365,15 @@ def run_ours_single(args) -> dict:
             "h2d_bytes_per_step": h2d_bytes,
             "d2h_bytes_per_step": d2h_bytes,
             "steps": e2e_steps,
+            "inputs": "CSR arrays and dense operands copied from pinned host memory every step",
+        },
+        "e2e_graph_resident": {
+            "value": round(algorithmic / (e2e_dense_ms * 1e-3) / 1e9, 2),
+            "unit": "GB/s",
+            "ms_per_step": round(e2e_dense_ms, 3),
+            "h2d_bytes_per_step": dense_bytes,
+            "d2h_bytes_per_step": d2h_bytes,
+            "inputs": "CSR arrays resident on the device; dense operands (and edge weights) copied every step",
         },
         # SpMM and SDDMM launch two kernels per step (main queues + the short-row queue), attention one
         "gpu_launches": args.steps * (1 if args.workload == "c4_attention" else 2),

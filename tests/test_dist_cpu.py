@@ -135,3 +135,38 @@ def test_sharded_conv_on_gloo_ranks(tmp_path, world, overlap, groups):
         assert torch.equal(p["weight"], weight)  # same seed, same layer on every rank
     expected = torch.from_numpy(exact).float() @ weight.t() + bias
     assert torch.allclose(torch.cat([p["out"] for p in parts]), expected, rtol=1e-4, atol=1e-4)
+
+
+def _failing_worker(rank: int, world: int, port: int, out_dir: str):
+    """Rank 1 leaves between steps (after a completed step, nothing in flight); rank 0 must get an
+    error from its next exchange instead of waiting forever."""
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    crow, col = random_csr(120, 6, seed=2)
+    x = dense(120, 8, 3)
+    bounds = asg_dist.partition_rows(crow, world)
+    shard = asg_dist.shard_csr(crow, col, None, rank, world, bounds)
+    layer = asg_dist.ShardedAutoSAGEConv(shard, 8, 4)
+    with torch.no_grad():
+        layer(x[shard.row_begin:shard.row_end])       # one good step on both ranks
+    dist.barrier()
+    if rank == 1:
+        dist.destroy_process_group()
+        return                                           # the peer is gone
+    outcome = "no error"
+    try:
+        with torch.no_grad():
+            layer(x[shard.row_begin:shard.row_end])
+    except Exception as exc:  # noqa: BLE001 - any error is the expected outcome
+        outcome = f"error: {type(exc).__name__}"
+    with open(os.path.join(out_dir, "rank0.txt"), "w") as handle:
+        handle.write(outcome)
+
+
+@pytest.mark.timeout(180)
+def test_a_departed_rank_surfaces_as_an_error_on_the_host(tmp_path):
+    mp.spawn(_failing_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "rank0.txt").read_text().startswith("error:")
