@@ -45,6 +45,7 @@ SIGNATURES = {
     "asg_sddmm_csr_ex": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_csr_row_softmax": (_INT, [_P, _P, _P, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_csr_attention": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _F32, _INT, _I64, _U32, _P, _SZ, _P]),
+    "asg_add_row_bias": (_INT, [_P, _P, _I64, _I64, _P]),
     "asg_workspace_status": (_INT, [_P, _P, _P]),
     "asg_spmm_csr_split_noalloc": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _P]),
     "asg_static_max_rows": (_I64, []),
@@ -233,6 +234,11 @@ def attention(crow, col, query, key, value, out, *, scale: float, warps: int, th
                                       value.data_ptr(), out.data_ptr(), query.size(0), col.numel(),
                                       query.size(1), float(scale), int(warps), int(threshold), int(flags),
                                       workspace.data_ptr(), workspace.numel(), _stream(query.device)))
+
+
+def add_row_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
+    """out[r, :] += bias, in place (contiguous float32 CUDA tensors)."""
+    check(library().asg_add_row_bias(out.data_ptr(), bias.data_ptr(), out.size(0), out.size(1), _stream(out.device)))
 
 
 def workspace_status(workspace: torch.Tensor) -> int:

@@ -22,10 +22,21 @@ def apply_linear(linear: nn.Linear, aggregated: torch.Tensor) -> torch.Tensor:
     """``linear(aggregated)``.  On CUDA float32 the product and the bias are issued separately
     (matmul, then an in-place add): cuBLAS's fused-bias SGEMM measured twice as slow as the plain one
     at these shapes on B200 (2.45 M x 128 -> 256: 6.1 ms against 3.2 ms), and the extra pass over the
-    output costs far less than that.  Same parameters, same float32 arithmetic, TF32 stays off."""
+    output (a copy-speed kernel of the library when no gradient is needed) costs far less than that.
+    Same parameters, same float32 arithmetic, TF32 stays off."""
     if aggregated.is_cuda and aggregated.dtype == torch.float32 and aggregated.dim() == 2:
         out = torch.mm(aggregated, linear.weight.t())
-        return out if linear.bias is None else out.add_(linear.bias)
+        if linear.bias is None:
+            return out
+        if torch.is_grad_enabled() and (out.requires_grad or linear.bias.requires_grad):
+            return out.add_(linear.bias)  # differentiable path
+        from . import _native
+        from .ops import load_native
+
+        if load_native() and linear.bias.dtype == torch.float32:
+            _native.add_row_bias(out, linear.bias.contiguous())
+            return out
+        return out.add_(linear.bias)
     return linear(aggregated)
 
 

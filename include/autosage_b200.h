@@ -142,6 +142,12 @@ int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, c
                       void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * out[rows, cols] += bias[cols] in place: the bias step of the layer's nn.Linear
+ * (autosage/conv.py:55), issued after a plain matrix product.
+ */
+int asg_add_row_bias(float* out, const float* bias, int64_t rows, int64_t cols, void* stream);
+
+/*
  * Status word written by kernels whose bounded waits gave up (0 = none).  The word lives in the
  * workspace header; this reads it back asynchronously into *host_status (pinned or pageable host
  * memory) on the given stream.  Non-zero means the output of the launch that set it is invalid.

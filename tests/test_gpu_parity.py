@@ -371,3 +371,45 @@ def test_full_size_attention_properties():
     err = (fused.double() - unfused.double()).abs()
     assert bool((err <= 2e-5 * unfused.abs().double() + 2e-5 * degree).all())
     assert set(info_f) >= {"sddmm", "spmm"} and set(info_u) >= {"sddmm", "spmm"}
+
+
+def test_offsets_beyond_32_bits(lib):
+    """N*F above 2^31 elements: the reference multiplies 32-bit ints when it indexes X and Y
+    (csrc/spmm_csr_vec4.cu:47,49); these kernels must not.  Few edges, so the check itself is cheap."""
+    n, f = 1_100_000, 2048                      # 2.25e9 elements per dense operand (9 GB each)
+    free, _ = torch.cuda.mem_get_info()
+    if free < 24 * 2**30:
+        pytest.skip("needs 24 GB of free device memory")
+    dev = torch.device("cuda")
+    rows = torch.tensor([0, 1, n // 2, n - 2, n - 1], device=dev)
+    cols = torch.tensor([n - 1, n - 1, 7, n // 2 + 3, n - 1], device=dev)
+    counts = torch.zeros(n, dtype=torch.long, device=dev)
+    counts[rows] = 1
+    crow = torch.zeros(n + 1, dtype=torch.long, device=dev)
+    torch.cumsum(counts, 0, out=crow[1:])
+    x = torch.zeros(n, f, device=dev)
+    for c in cols.unique().tolist():
+        x[c] = torch.arange(f, device=dev, dtype=torch.float32) + float(c % 1000)
+    y = torch.full((n, f), float("nan"), device=dev)
+    ws = torch.empty(lib.workspace_bytes(n), dtype=torch.uint8, device=dev)
+    lib.spmm(crow, cols, None, x, y, feature_tile=128, warps=8, threshold=64, flags=0, workspace=ws)
+    torch.cuda.synchronize()
+    for r, c in zip(rows.tolist(), cols.tolist()):
+        assert torch.equal(y[r], x[c]), (r, c)
+    assert float(y[3].abs().max()) == 0.0 and float(y[n - 3].abs().max()) == 0.0   # empty rows are zeroed
+    out = torch.empty(5, device=dev)
+    lib.sddmm(crow, cols, x, x, out, warps=8, threshold=64, flags=0, workspace=ws)
+    torch.cuda.synchronize()
+    expected = torch.stack([(x[r].double() * x[c].double()).sum() for r, c in zip(rows.tolist(), cols.tolist())])
+    assert torch.allclose(out.double(), expected, rtol=1e-5)
+
+
+def test_row_bias_epilogue(lib):
+    for rows, cols, offset in ((1000, 256, 0), (333, 100, 0), (77, 5, 0), (64, 64, 1)):
+        out = dense(rows, cols, 1).cuda()
+        bias = dense(1, cols + offset, 2).flatten().cuda()[offset:]   # offset 1: misaligned -> scalar path
+        expected = out + bias
+        lib.add_row_bias(out, bias.contiguous() if offset == 0 else bias)
+        torch.cuda.synchronize()
+        assert torch.equal(out, expected)
+    lib.check(lib.library().asg_add_row_bias(None, None, 0, 16, None))
