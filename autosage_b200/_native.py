@@ -22,6 +22,7 @@ FLAG_ACCUMULATE = 1
 FLAG_NO_VEC4 = 2
 FLAG_PLAN_READY = 4
 FLAG_NO_BULK_STAGE = 8
+FLAG_NO_TILE_PASSES = 16
 
 _P = ctypes.c_void_p
 _I64 = ctypes.c_int64

@@ -26,7 +26,10 @@ struct SddmmArgs {
   const int* order;
   int f;
   int n_tiles;
+  int fixed_tile;  // >= 0: this launch covers only that feature tile and, for tile > 0, adds to out
 };
+
+constexpr int kTilePasses = -2;  // SddmmArgs::fixed_tile on the host side: "launch once per tile"
 
 template <int VW, int G, int NV, int U>
 __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, long long first, long long stride,
@@ -55,7 +58,8 @@ __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, l
       }
     }
   };
-  if (a.n_tiles == 1) load_q(0);
+  const bool one_tile = a.n_tiles == 1 || a.fixed_tile >= 0;
+  if (one_tile) load_q(a.fixed_tile >= 0 ? a.fixed_tile : 0);
 
   for (long long p = first; p < e; p += stride) {
     const int cnt = e - p < 32 ? static_cast<int>(e - p) : 32;
@@ -64,7 +68,7 @@ __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, l
     float part[G];
 #pragma unroll
     for (int i = 0; i < G; ++i) part[i] = 0.f;
-    if (a.n_tiles == 1) {
+    if (one_tile) {
       batch_dots<VW, G, NV, U, false>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
     } else {
       for (int tile = 0; tile < a.n_tiles; ++tile) {
@@ -72,9 +76,12 @@ __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, l
         batch_dots<VW, G, NV, U, false>(a.k, f, c_l, cnt, sub, q, fvalid, foff, pol_keep, part);
       }
     }
-    const float dot = group_reduce_scatter<G>(part, l);
+    float dot = group_reduce_scatter<G>(part, l);
     const int edge = l * EPI + sub;
-    if (edge < cnt) st_stream1(a.out + p + edge, dot);
+    if (edge < cnt) {
+      if (a.fixed_tile > 0) dot += a.out[p + edge];  // partial sum of the earlier tiles (earlier launches)
+      st_stream1(a.out + p + edge, dot);
+    }
   }
 }
 
@@ -206,8 +213,22 @@ static int launch_instance(const SddmmArgs& args, int warps, cudaStream_t stream
   int per_sm = 0;
   ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
   if (per_sm < 1) per_sm = 1;
-  kernel<<<sm_count(device) * per_sm, threads, 0, stream>>>(args);
-  ASG_CUDA(cudaGetLastError());
+  if (args.fixed_tile == kTilePasses) {
+    // One launch per feature tile, tile 0 first: while a pass runs only an N x FT slice of K is hot
+    // in L2.  Partial sums travel through `out`; stream order makes pass t see pass t-1.
+    SddmmArgs pass = args;
+    for (int t = 0; t < args.n_tiles; ++t) {
+      if (t > 0) {
+        if (int rc = reset_counters(args.header, stream)) return rc;
+      }
+      pass.fixed_tile = t;
+      kernel<<<sm_count(device) * per_sm, threads, 0, stream>>>(pass);
+      ASG_CUDA(cudaGetLastError());
+    }
+  } else {
+    kernel<<<sm_count(device) * per_sm, threads, 0, stream>>>(args);
+    ASG_CUDA(cudaGetLastError());
+  }
   auto short_kernel = sddmm_short_kernel<VW, G, NV, U>;
   int short_per_sm = 0;
   ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&short_per_sm, short_kernel, threads, 0));
@@ -221,12 +242,20 @@ static int launch_instance(const SddmmArgs& args, int warps, cudaStream_t stream
 #define ASG_SDDMM_U 8
 #endif
 
+// K larger than this (bytes) no longer sits comfortably in L2 next to the streamed CSR and output:
+// the product is then computed in passes of 64 features.
+constexpr long long kTilePassBytes = 64ll << 20;
+
 // Picks the narrowest tile that covers f (so Q stays in registers); above 512 floats the tile is
 // 512 wide and Q is re-read per batch.
 static int launch_sddmm(SddmmArgs& args, int vw, cudaStream_t stream, int warps, int device) {
   constexpr int U = ASG_SDDMM_U;
   const int f = args.f;
   auto tiles = [&](int ft) { args.n_tiles = (f + ft - 1) / ft; };
+  if (vw == 8 && args.fixed_tile == kTilePasses) {
+    tiles(64);
+    return launch_instance<8, 8, 1, U / 2>(args, warps, stream, device);
+  }
   if (vw == 8) {
     if (f <= 32) { tiles(32); return launch_instance<8, 4, 1, U / 2>(args, warps, stream, device); }
     if (f <= 64) { tiles(64); return launch_instance<8, 8, 1, U / 2>(args, warps, stream, device); }
@@ -294,6 +323,9 @@ static int sddmm_entry(const int64_t* crow, const int64_t* col, const float* q, 
   args.order = reinterpret_cast<const int*>(static_cast<const char*>(workspace) + order_offset());
   args.f = static_cast<int>(f);
   args.n_tiles = 1;
+  const bool passes = vw == 8 && f >= 128 && f % 64 == 0 && !(flags & ASG_FLAG_NO_TILE_PASSES) &&
+                      static_cast<long long>(n_rows) * f * 4 > kTilePassBytes;
+  args.fixed_tile = passes ? kTilePasses : -1;
   return launch_sddmm(args, vw, stream, warps, guard.target);
 }
 

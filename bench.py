@@ -357,6 +357,8 @@ def run_ours_single(args) -> dict:
             "note": "achieved counts every gathered dense row (CSR + gathered rows + output); when the dense operand "
                     "fits the 126 MB L2 the gather is served by L2 and achieved exceeds the HBM peak",
             "launch_ms": round(launch_ms, 4),
+            "launch_ms_median_min_max": [round(statistics.median(per_launch), 4), round(min(per_launch), 4),
+                                         round(max(per_launch), 4)],
         },
         "e2e": {
             "value": round(algorithmic / (e2e_ms * 1e-3) / 1e9, 2),
@@ -379,6 +381,24 @@ def run_ours_single(args) -> dict:
         "gpu_launches": args.steps * (1 if args.workload == "c4_attention" else 2),
         "clocks": clocks.summary(),
     }
+
+    if args.workload in ("c2_spmm", "c5_spmm"):
+        # the reference's own GPU baseline on this box: cuSPARSE through torch.sparse.mm (library call)
+        weights = w["val"] if w.get("val") is not None else torch.ones(nnz, device=device)
+        matrix = torch.sparse_csr_tensor(crow, col, weights, size=(n, n))
+        torch.sparse.mm(matrix, w["x"])
+        torch.cuda.synchronize()
+        c_begin, c_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c_begin.record(stream)
+        for _ in range(3):
+            torch.sparse.mm(matrix, w["x"])
+        c_end.record(stream)
+        torch.cuda.synchronize()
+        cusparse_ms = c_begin.elapsed_time(c_end) / 3
+        line["gpu_comparator"] = {"name": "torch.sparse.mm (cuSPARSE), the reference scheduler's baseline",
+                                  "ms_per_step": round(cusparse_ms, 4),
+                                  "value": round(algorithmic / (cusparse_ms * 1e-3) / 1e9, 2), "unit": "GB/s"}
+        del matrix, weights
 
     if not args.no_cpu_baseline and args.workload in ("c2_spmm", "c5_spmm"):
         from oracle import oracle

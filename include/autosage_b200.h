@@ -52,6 +52,7 @@ extern "C" {
 #define ASG_FLAG_NO_VEC4 2u    /* force the scalar kernels (AUTOSAGE_VEC4=0 in the reference) */
 #define ASG_FLAG_PLAN_READY 4u /* workspace already holds a plan for this crow/threshold */
 #define ASG_FLAG_NO_BULK_STAGE 8u /* hub rows: stage col/val with plain loads, not bulk copies */
+#define ASG_FLAG_NO_TILE_PASSES 16u /* SDDMM: never split the feature dimension into 64-wide passes */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int asg_version(void);

@@ -413,3 +413,21 @@ def test_row_bias_epilogue(lib):
         torch.cuda.synchronize()
         assert torch.equal(out, expected)
     lib.check(lib.library().asg_add_row_bias(None, None, 0, 16, None))
+
+
+def test_sddmm_feature_passes_on_a_large_key_matrix(lib, orc):
+    """K above 64 MB switches SDDMM to one launch per 64-feature tile with partial sums kept in the
+    output; the result must match the oracle and the single-launch form."""
+    n, f = 140_000, 128                                  # K = 71.7 MB
+    gen = torch.Generator().manual_seed(5)
+    counts = torch.randint(0, 5, (n,), generator=gen)
+    counts[100], counts[70_000], counts[139_999] = 3000, 900, 40   # a hub, two medium rows
+    crow, col = csr_from_counts(counts, n, seed=6)
+    q, k = dense(n, f, 7), dense(n, f, 8)
+    exact = orc.sddmm(to_np(crow), to_np(col), to_np(q), to_np(k))
+    tiled = run_sddmm(lib, crow, col, q, k, warps=8, threshold=1024)
+    single = run_sddmm(lib, crow, col, q, k, warps=8, threshold=1024, flags=lib.FLAG_NO_TILE_PASSES)
+    for out in (tiled, single):
+        ok, ratio = orc.within_tolerance(out.cpu().numpy(), exact, to_np(crow), per_edge=True, rtol=RTOL, atol=ATOL)
+        assert ok, f"worst error/bound {ratio:.3f}"
+    assert not torch.isnan(tiled).any()
