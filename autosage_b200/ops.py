@@ -10,6 +10,7 @@ defined from Python with ``torch.library`` and implemented by calls into the C A
 from __future__ import annotations
 
 import os
+import weakref
 from typing import Optional
 
 import torch
@@ -149,8 +150,6 @@ _TRANSPOSES: dict[tuple, tuple] = {}
 def _transposed_pattern(crow: torch.Tensor, col: torch.Tensor):
     """(crow_t, col_t, perm) of the transposed square pattern; perm[i] is the position in the original
     edge order of the i-th edge of the transpose.  Memoised per (crow, col) tensor pair."""
-    import weakref
-
     key = (crow.data_ptr(), col.data_ptr(), crow.numel(), col.numel())
     hit = _TRANSPOSES.get(key)
     if hit is not None and hit[0]() is crow and hit[1]() is col and hit[2] == (crow._version, col._version):

@@ -60,10 +60,6 @@ def _f32(a) -> np.ndarray:
     return np.ascontiguousarray(np.asarray(a), dtype=np.float32)
 
 
-def _optional_f32(a):
-    return None if a is None else _f32(a).ctypes.data_as(ctypes.c_void_p)
-
-
 def spmm(crow, col, val, x, *, dtype=np.float64) -> np.ndarray:
     """Y = A X with A in CSR (autosage/ops.py:124-143, torch.sparse.mm on a CSR tensor).
     dtype float64 accumulates in double (accuracy oracle); float32 is the reference's CPU arithmetic."""
