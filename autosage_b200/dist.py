@@ -204,7 +204,7 @@ class ShardedSpmm:
 
     def __init__(self, shard: RowShard, features: int, *, group=None, dtype=torch.float32, feature_tile: int = 128,
                  warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
-                 exchange: Optional[str] = None) -> None:
+                 exchange: Optional[str] = None, copy_streams: int = 1) -> None:
         self.shard = shard
         self.group = group
         self.features = features
@@ -214,6 +214,9 @@ class ShardedSpmm:
         if device.type == "cuda" and not load_native():
             raise RuntimeError("libautosage_b200.so is required for the CUDA path")
         self.comm_stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        # further streams for the pulls (peer mode): consecutive sources alternate between them
+        self.copy_streams = ([torch.cuda.Stream(device=device) for _ in range(max(0, int(copy_streams) - 1))]
+                             if device.type == "cuda" else [])
         self.handle = None
         self.x_full = None
         wanted = exchange or os.getenv("AUTOSAGE_EXCHANGE", "peer" if device.type == "cuda" else "nccl")
@@ -225,6 +228,7 @@ class ShardedSpmm:
         if not shard.groups:
             shard.groups = [[k] for k in arrival_order(shard.rank, shard.world)]
         self._events = [torch.cuda.Event() for _ in range(shard.world)] if device.type == "cuda" else []
+        self._opened = torch.cuda.Event() if device.type == "cuda" else None
 
     def _try_symmetric(self, dtype) -> None:
         """Allocate X in symmetric memory and map the peers' copies; all ranks agree on the outcome."""
@@ -272,10 +276,22 @@ class ShardedSpmm:
         """Peer mode, on the communication stream: barrier, one copy-engine pull per source in
         arrival order (an event after each), barrier."""
         shard = self.shard
+        main = self.comm_stream
         self.handle.barrier(channel=0)
-        for owner in arrival_order(shard.rank, shard.world)[1:]:
-            self._shard_view(owner).copy_(self._peers[owner], non_blocking=True)
-            self._events[owner].record(self.comm_stream)
+        streams = [main] + self.copy_streams
+        if self.copy_streams:
+            self._opened.record(main)
+            for extra in self.copy_streams:
+                extra.wait_event(self._opened)
+        sources = arrival_order(shard.rank, shard.world)[1:]
+        for i, owner in enumerate(sources):
+            stream = streams[i % len(streams)]
+            with torch.cuda.stream(stream):
+                self._shard_view(owner).copy_(self._peers[owner], non_blocking=True)
+                self._events[owner].record(stream)
+        if self.copy_streams:
+            for owner in sources:
+                main.wait_event(self._events[owner])
         self.handle.barrier(channel=1)
 
     def exchange_only(self) -> None:
@@ -311,9 +327,10 @@ class ShardedSpmm:
             if not overlap:
                 current.wait_stream(self.comm_stream)
             for g, (block, members) in enumerate(zip(shard.blocks, shard.groups)):
-                last = members[-1]
-                if overlap and last != shard.rank:
-                    current.wait_event(self._events[last])
+                if overlap:
+                    for member in members:
+                        if member != shard.rank:
+                            current.wait_event(self._events[member])
                 _block_spmm(block, self.x_full, y, g > 0, **kw)
             # the closing barrier of the exchange must be part of this step's stream order
             current.wait_stream(self.comm_stream)
@@ -347,11 +364,11 @@ class ShardedAutoSAGEConv(torch.nn.Module):
 
     def __init__(self, shard: RowShard, in_channels: int, out_channels: int, *, bias: bool = True, group=None,
                  feature_tile: int = 128, warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
-                 exchange: Optional[str] = None) -> None:
+                 exchange: Optional[str] = None, copy_streams: int = 1) -> None:
         super().__init__()
         self.linear = torch.nn.Linear(in_channels, out_channels, bias=bias)
         self.spmm = ShardedSpmm(shard, in_channels, group=group, feature_tile=feature_tile, warps=warps,
-                                threshold=threshold, exchange=exchange)
+                                threshold=threshold, exchange=exchange, copy_streams=copy_streams)
 
     def forward(self, x_local: Optional[torch.Tensor] = None, overlap: bool = True) -> torch.Tensor:
         if x_local is not None and x_local.data_ptr() != self.spmm.x_local.data_ptr():

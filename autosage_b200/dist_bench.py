@@ -55,7 +55,7 @@ def run(args):
     crow, col, info = syn.powerlaw_csr(spec, seed=0, device=device)
     n, nnz = info["rows"], info["nnz"]
     bounds = asg_dist.partition_rows(crow, world)
-    shard = asg_dist.shard_csr(crow, col, None, rank, world, bounds, groups=args.groups)
+    shard = asg_dist.shard_csr(crow, col, None, rank, world, bounds, groups=args.groups if args.groups else min(world, 4))
 
     # The same layer on ONE GPU (no sharding, no exchange), timed inside this job so that every
     # multi-GPU line carries its own strong-scaling reference.  Every rank times it on its own GPU
@@ -85,7 +85,8 @@ def run(args):
 
     torch.manual_seed(0)
     layer = asg_dist.ShardedAutoSAGEConv(shard, f, out_f, bias=True, feature_tile=args.tile, warps=args.warps,
-                                         threshold=args.hub_threshold, exchange=args.exchange).to(device)
+                                         threshold=args.hub_threshold, exchange=args.exchange,
+                                         copy_streams=args.copy_streams).to(device)
     torch.nn.init.xavier_uniform_(layer.linear.weight)
     torch.nn.init.zeros_(layer.linear.bias)
     gen = torch.Generator(device=device).manual_seed(3)

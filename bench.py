@@ -505,6 +505,7 @@ def main() -> None:
     parser.add_argument("--cpu-sample-nnz", type=int, default=4_000_000)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--groups", type=int, default=None, help="column groups per GPU in the sharded path")
+    parser.add_argument("--copy-streams", type=int, default=1, help="streams used for the peer pulls (sharded path)")
     parser.add_argument("--exchange", default=None, choices=["peer", "nccl"], help="how X is gathered (sharded path)")
     args = parser.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))

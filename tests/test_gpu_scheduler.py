@@ -263,3 +263,36 @@ def test_operators_are_differentiable(asg, isolated_cache):
     assert set(info) == {"sddmm", "spmm"}
     out.sum().backward()
     assert qq.grad is not None and torch.isfinite(qq.grad).all()
+
+
+def test_operators_replay_inside_a_cuda_graph(asg, orc):
+    """Small graphs are launch-bound; the operators must be capturable (no allocation inside the
+    library, no host synchronisation) so that a layer's steady state can be replayed as a CUDA graph."""
+    crow, col = random_csr(4000, 10, seed=31, hubs={9: 3000})
+    val = weights(col.numel(), 2)
+    x = dense(4000, 64, 3)
+    crow_d, col_d, val_d, x_d = (t.cuda() for t in (crow, col, val, x))
+    q_d, k_d = dense(4000, 64, 4).cuda(), dense(4000, 64, 5).cuda()
+    # warm up on a side stream (builds the plans, loads the kernels), then capture
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            torch.ops.autosage.spmm_csr_split(crow_d, col_d, val_d, x_d, 64, 4, 256)
+            torch.ops.autosage.sddmm_csr_split(crow_d, col_d, q_d, k_d, 4, 256)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y = torch.ops.autosage.spmm_csr_split(crow_d, col_d, val_d, x_d, 64, 4, 256)
+        s = torch.ops.autosage.sddmm_csr_split(crow_d, col_d, q_d, k_d, 4, 256)
+    for trial in range(3):
+        x_d.copy_(dense(4000, 64, 10 + trial))          # new inputs, same buffers
+        graph.replay()
+        torch.cuda.synchronize()
+        exact = orc.spmm(to_np(crow), to_np(col), to_np(val), x_d.cpu().numpy())
+        ok, ratio = orc.within_tolerance(y.cpu().numpy(), exact, to_np(crow))
+        assert ok, ratio
+    exact_s = orc.sddmm(to_np(crow), to_np(col), q_d.cpu().numpy(), k_d.cpu().numpy())
+    ok, ratio = orc.within_tolerance(s.cpu().numpy(), exact_s, to_np(crow), per_edge=True)
+    assert ok, ratio
