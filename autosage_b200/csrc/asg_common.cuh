@@ -192,8 +192,33 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
       "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
+// ---- programmatic dependent launch ------------------------------------------------------------
+// A kernel launched with launch_overlapped() may start while the kernel before it on the stream is
+// still running (as soon as every CTA of that kernel has executed pdl_release_dependents() or has
+// exited).  It must call pdl_wait_for_primary() before it ends, so that whatever follows on the
+// stream still sees both kernels complete.  Used for the short-row kernels, which touch rows the main
+// kernel never touches: they fill the SMs the main kernel's last long rows leave idle.
+__device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_for_primary() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+template <typename Args>
+inline cudaError_t launch_overlapped(void (*kernel)(Args), int grid, int threads, size_t smem, cudaStream_t stream,
+                                     const Args& args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(grid));
+  config.blockDim = dim3(static_cast<unsigned>(threads));
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, args);
 }
 
 #endif  // __CUDACC__

@@ -92,6 +92,7 @@ __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, l
 #endif
 template <int VW, int G, int NV, int U>
 __global__ void ASG_BOUNDS sddmm_kernel(const SddmmArgs a) {
+  pdl_release_dependents();  // the short-row kernel may move in as CTAs of this one retire
   __shared__ int s_item;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -204,6 +205,7 @@ __global__ void __launch_bounds__(512) sddmm_short_kernel(const SddmmArgs a) {
       }
     }
   }
+  pdl_wait_for_primary();  // do not complete before the main kernel has
 }
 
 template <int VW, int G, int NV, int U>
@@ -233,8 +235,7 @@ static int launch_instance(const SddmmArgs& args, int warps, cudaStream_t stream
   int short_per_sm = 0;
   ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&short_per_sm, short_kernel, threads, 0));
   if (short_per_sm < 1) short_per_sm = 1;
-  short_kernel<<<sm_count(device) * short_per_sm, threads, 0, stream>>>(args);
-  ASG_CUDA(cudaGetLastError());
+  ASG_CUDA(launch_overlapped(short_kernel, sm_count(device) * short_per_sm, threads, 0, stream, args));
   return ASG_OK;
 }
 

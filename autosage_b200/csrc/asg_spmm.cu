@@ -41,9 +41,10 @@ constexpr int kChunkPerWarp = 128;  // staged edges per warp and stage in the hu
 // latency-bound when taken one at a time (queue grab, row id, two row pointers, columns, X rows,
 // output: five dependent memory round trips for a handful of edges).  Here a warp reads the ids
 // and pointers of 32 rows with one coalesced load each and walks them with the next row's columns
-// already in flight.  It runs as a kernel of its own (launched right after the main one) so that its
-// registers and schedule do not disturb the long-row loops: inlined into the main kernel it cost the
-// long-row workloads about 10 %.
+// already in flight.  It runs as a kernel of its own so that its registers and schedule do not disturb
+// the long-row loops (inlined into the main kernel it cost the long-row workloads about 10 %), launched
+// right after the main kernel as a programmatic dependent: it starts filling SMs as the main kernel's
+// CTAs retire instead of waiting for its last hub row.
 template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL>
 __device__ __forceinline__ void spmm_short_rows(const SpmmArgs& a, int n_hub, int n_medium, int n_short) {
   constexpr int U = U_REQUESTED < G ? U_REQUESTED : G;
@@ -512,10 +513,12 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
 // measured 10 % faster when the gathered rows come from HBM (whole-row 128-float tiles).
 template <int VW, int G, int NV, int U, bool HAS_VAL>
 __global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
+  pdl_release_dependents();  // the short-row kernel may move in as CTAs of this one retire
   spmm_body<VW, G, NV, U, HAS_VAL>(a);
 }
 template <int VW, int G, int NV, int U, bool HAS_VAL>
 __global__ void __launch_bounds__(512, 1) spmm_kernel_deep(const SpmmArgs a) {
+  pdl_release_dependents();
   spmm_body<VW, G, NV, U, HAS_VAL>(a);
 }
 
@@ -524,6 +527,7 @@ __global__ void __launch_bounds__(512) spmm_short_kernel(const SpmmArgs a) {
   const int n_hub = a.header->n_hub;
   const int n_short = a.header->n_short;
   if (n_short > 0) spmm_short_rows<VW, G, NV, U, HAS_VAL>(a, n_hub, a.header->n_light - n_short, n_short);
+  pdl_wait_for_primary();  // do not complete before the main kernel has
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -552,8 +556,7 @@ static int launch_instance(const SpmmArgs& args, int warps, cudaStream_t stream,
   int short_per_sm = 0;
   ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&short_per_sm, short_kernel, threads, 0));
   if (short_per_sm < 1) short_per_sm = 1;
-  short_kernel<<<sm_count(device) * short_per_sm, threads, 0, stream>>>(args);
-  ASG_CUDA(cudaGetLastError());
+  ASG_CUDA(launch_overlapped(short_kernel, sm_count(device) * short_per_sm, threads, 0, stream, args));
   return ASG_OK;
 }
 
