@@ -41,12 +41,14 @@ SIGNATURES = {
     "asg_spmm_csr": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
     "asg_spmm_csr_split": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _P, _SZ, _P]),
     "asg_spmm_csr_ex": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _U32, _P, _SZ, _P]),
+    "asg_spmm_csr_range": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _INT, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_sddmm_csr": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
     "asg_sddmm_csr_split": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _I64, _P, _SZ, _P]),
     "asg_sddmm_csr_ex": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_csr_row_softmax": (_INT, [_P, _P, _P, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_csr_attention": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _F32, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_add_row_bias": (_INT, [_P, _P, _I64, _I64, _P]),
+    "asg_copy_2d": (_INT, [_P, _SZ, _P, _SZ, _SZ, _SZ, _P]),
     "asg_workspace_status": (_INT, [_P, _P, _P]),
     "asg_spmm_csr_split_noalloc": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _P]),
     "asg_static_max_rows": (_I64, []),
@@ -188,6 +190,24 @@ def spmm(crow, col, val, x, y, *, feature_tile: int, warps: int, threshold: int,
                                     y.size(0), col.numel(), x.size(1), int(feature_tile), int(warps),
                                     int(threshold), int(flags), workspace.data_ptr(), workspace.numel(),
                                     _stream(x.device)))
+
+
+def spmm_range(crow, col, val, x, y, *, feature_begin: int, feature_count: int, feature_tile: int, warps: int,
+               threshold: int, flags: int, workspace: torch.Tensor) -> None:
+    """SpMM restricted to the output columns [feature_begin, feature_begin + feature_count)."""
+    check(library().asg_spmm_csr_range(crow.data_ptr(), col.data_ptr(), _ptr(val), x.data_ptr(), y.data_ptr(),
+                                       y.size(0), col.numel(), x.size(1), int(feature_begin), int(feature_count),
+                                       int(feature_tile), int(warps), int(threshold), int(flags),
+                                       workspace.data_ptr(), workspace.numel(), _stream(x.device)))
+
+
+def copy_columns(dst: torch.Tensor, src: torch.Tensor, column_begin: int, column_count: int) -> None:
+    """dst[:, c0:c0+n] = src[:, c0:c0+n] for two row-major 2-D tensors of equal shape, as one pitched
+    copy on the current stream (copy engines; src may be a peer-mapped tensor of another GPU)."""
+    item = dst.element_size()
+    offset = int(column_begin) * item
+    check(library().asg_copy_2d(dst.data_ptr() + offset, dst.stride(0) * item, src.data_ptr() + offset,
+                                src.stride(0) * item, int(column_count) * item, dst.size(0), _stream(dst.device)))
 
 
 def spmm_split_strict(crow, col, val, x, y, feature_tile: int, warps: int, threshold: int,

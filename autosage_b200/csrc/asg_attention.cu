@@ -218,9 +218,6 @@ __device__ __forceinline__ void attention_batches(const AttentionArgs& a, int ro
   }
 }
 
-template <int VW, int G, int NV, int U>
-__device__ __forceinline__ void attention_short_rows(const AttentionArgs& a);
-
 #ifdef ASG_ATTN_MIN_BLOCKS  // e.g. 2 caps the kernel at 64 registers per thread
 #define ASG_BOUNDS __launch_bounds__(512, ASG_ATTN_MIN_BLOCKS)
 #else
@@ -228,6 +225,7 @@ __device__ __forceinline__ void attention_short_rows(const AttentionArgs& a);
 #endif
 template <int VW, int G, int NV, int U>
 __global__ void ASG_BOUNDS attention_kernel(const AttentionArgs a) {
+  pdl_release_dependents();  // the short-row kernel may move in as CTAs of this one retire
   constexpr int FT = VW * G * NV;
   extern __shared__ __align__(16) unsigned char smem[];
   int* s_item = reinterpret_cast<int*>(smem);
@@ -334,16 +332,15 @@ __global__ void ASG_BOUNDS attention_kernel(const AttentionArgs a) {
       }
     }
   }
-  attention_short_rows<VW, G, NV, U>(a);
 }
 
 // Queue 2: light rows of fewer than 32 edges.  A warp grabs 32 of them, reads ids and row pointers
 // with coalesced loads and walks them with the next row's columns already in flight; one batch per
-// row, so the online-softmax state never needs rescaling.  It stays inside the main kernel: the longest
-// hub rows keep a few CTAs busy for a long time and these rows are what the rest of the GPU does
-// meanwhile (as a kernel of its own, launched afterwards, it measured 30 % slower end to end).
+// row, so the online-softmax state never needs rescaling.  A kernel of its own (72 registers against
+// the main kernel's 128, so more warps in flight for these latency-bound rows), launched as a
+// programmatic dependent of the main kernel: it fills the SMs while the longest hub rows finish.
 template <int VW, int G, int NV, int U>
-__device__ __forceinline__ void attention_short_rows(const AttentionArgs& a) {
+__global__ void __launch_bounds__(512) attention_short_kernel(const AttentionArgs a) {
   const int lane = threadIdx.x & 31;
   const int l = lane % G;
   const int sub = lane / G;
@@ -416,6 +413,7 @@ __device__ __forceinline__ void attention_short_rows(const AttentionArgs& a) {
       }
     }
   }
+  pdl_wait_for_primary();  // do not complete before the main kernel has
 }
 
 template <int VW, int G, int NV, int U>
@@ -431,6 +429,11 @@ static int launch_attention_instance(const AttentionArgs& args, int warps, cudaS
   if (per_sm < 1) per_sm = 1;
   kernel<<<sm_count(device) * per_sm, threads, smem, stream>>>(args);
   ASG_CUDA(cudaGetLastError());
+  auto short_kernel = attention_short_kernel<VW, G, NV, U>;
+  int short_per_sm = 0;
+  ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&short_per_sm, short_kernel, threads, 0));
+  if (short_per_sm < 1) short_per_sm = 1;
+  ASG_CUDA(launch_overlapped(short_kernel, sm_count(device) * short_per_sm, threads, 0, stream, args));
   return ASG_OK;
 }
 

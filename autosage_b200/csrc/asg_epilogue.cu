@@ -53,3 +53,18 @@ extern "C" int asg_add_row_bias(float* out, const float* bias, int64_t rows, int
   ASG_CUDA(cudaGetLastError());
   return ASG_OK;
 }
+
+// Pitched device-to-device copy (cudaMemcpy2DAsync: copy engines, no kernel).  The sharded path uses it
+// to pull a band of feature columns of another GPU's rows out of its peer-mapped X.
+extern "C" int asg_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                           size_t height, void* stream_ptr) {
+  using namespace asg;
+  if (width_bytes == 0 || height == 0) return ASG_OK;
+  ASG_REQUIRE(dst != nullptr && src != nullptr, ASG_EINVAL, "dst and src must not be null");
+  ASG_REQUIRE(dst_pitch >= width_bytes && src_pitch >= width_bytes, ASG_EINVAL, "pitch smaller than the row width");
+  DeviceGuard guard(dst);
+  ASG_CUDA(guard.status);
+  ASG_CUDA(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, height, cudaMemcpyDefault,
+                             static_cast<cudaStream_t>(stream_ptr)));
+  return ASG_OK;
+}

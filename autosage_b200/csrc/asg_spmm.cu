@@ -30,7 +30,8 @@ struct SpmmArgs {
   Header* header;
   const int* order;
   int f;
-  int n_tiles;
+  int n_tiles;      // feature tiles this launch covers
+  int tile_begin;   // index of the first of them (0 unless a feature range was requested)
   int accumulate;
   int bulk_stage;
 };
@@ -67,7 +68,7 @@ __device__ __forceinline__ void spmm_short_rows(const SpmmArgs& a, int n_hub, in
       const int tile = static_cast<int>(it / n_batches);
       const int first = static_cast<int>(it - static_cast<unsigned long long>(tile) * n_batches) * 32;
       const int n_here = n_short - first < 32 ? n_short - first : 32;
-      const int fbase = tile * FT;
+      const int fbase = (a.tile_begin + tile) * FT;
       int row_l = 0;
       long long s_l = 0, e_l = 0;
       if (lane < n_here) {
@@ -216,7 +217,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
       if (item < 0) break;
       const int tile = item / n_hub;
       const int row = a.order[item - tile * n_hub];
-      const int fbase = tile * FT;
+      const int fbase = (a.tile_begin + tile) * FT;
       const long long s = a.crow[row];
       const long long e = a.crow[row + 1];
       const long long a0 = s & ~3ll;  // staging starts on a 4-edge boundary (32 B of col, 16 B of val)
@@ -393,7 +394,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
       if (it >= static_cast<unsigned long long>(total)) break;
       const int tile = static_cast<int>(it / n_medium);
       const int row = light[it - static_cast<unsigned long long>(tile) * n_medium];
-      const int fbase = tile * FT;
+      const int fbase = (a.tile_begin + tile) * FT;
       const long long s = a.crow[row];
       const long long e = a.crow[row + 1];
 
@@ -606,7 +607,8 @@ static bool aligned_to(const void* p, size_t n) { return (reinterpret_cast<uintp
 
 static int spmm_entry(const int64_t* crow, const int64_t* col, const float* val, const float* x, float* y,
                       int64_t n_rows, int64_t nnz, int64_t f, int feature_tile, int warps, int64_t hub_threshold,
-                      unsigned flags, void* workspace, size_t workspace_bytes, void* stream_ptr) {
+                      unsigned flags, void* workspace, size_t workspace_bytes, void* stream_ptr,
+                      int64_t feature_begin = 0, int64_t feature_count = 0) {
   ASG_REQUIRE(n_rows >= 0 && nnz >= 0 && f >= 0, ASG_EINVAL, "sizes must be non-negative");
   ASG_REQUIRE(n_rows <= 2147483647ll - 2048 && f <= 2147483647ll, ASG_ERANGE,
               "SpMM dimensions exceed the kernel index range");
@@ -649,6 +651,15 @@ static int spmm_entry(const int64_t* crow, const int64_t* col, const float* val,
   args.order = reinterpret_cast<const int*>(static_cast<const char*>(workspace) + order_offset());
   args.f = static_cast<int>(f);
   args.n_tiles = static_cast<int>((f + feature_tile - 1) / feature_tile);
+  args.tile_begin = 0;
+  if (feature_count > 0) {  // only the columns [feature_begin, feature_begin + feature_count) of y
+    ASG_REQUIRE(feature_begin >= 0 && feature_begin + feature_count <= f, ASG_EINVAL, "feature range exceeds f");
+    ASG_REQUIRE(feature_begin % feature_tile == 0 &&
+                    (feature_count % feature_tile == 0 || feature_begin + feature_count == f),
+                ASG_EINVAL, "feature range must start and end on a feature_tile boundary (or at f)");
+    args.tile_begin = static_cast<int>(feature_begin / feature_tile);
+    args.n_tiles = static_cast<int>((feature_count + feature_tile - 1) / feature_tile);
+  }
   args.accumulate = (flags & ASG_FLAG_ACCUMULATE) ? 1 : 0;
   args.bulk_stage = (!(flags & ASG_FLAG_NO_BULK_STAGE) && aligned_to(col, 16) && (val == nullptr || aligned_to(val, 16))) ? 1 : 0;
   return launch_spmm(args, vw, feature_tile, warps, stream, guard.target);
@@ -663,6 +674,15 @@ int asg_spmm_csr_ex(const int64_t* crow, const int64_t* col, const float* val, c
                     int64_t hub_threshold, unsigned flags, void* workspace, size_t workspace_bytes, void* stream) {
   return asg::spmm_entry(crow, col, val, x, y, n_rows, nnz, f, feature_tile, warps_per_block, hub_threshold, flags,
                          workspace, workspace_bytes, stream);
+}
+
+int asg_spmm_csr_range(const int64_t* crow, const int64_t* col, const float* val, const float* x, float* y,
+                       int64_t n_rows, int64_t nnz, int64_t f, int64_t feature_begin, int64_t feature_count,
+                       int feature_tile, int warps_per_block, int64_t hub_threshold, unsigned flags, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+  if (feature_count <= 0) return asg::fail(ASG_EINVAL, "%s", "feature_count must be positive");
+  return asg::spmm_entry(crow, col, val, x, y, n_rows, nnz, f, feature_tile, warps_per_block, hub_threshold, flags,
+                         workspace, workspace_bytes, stream, feature_begin, feature_count);
 }
 
 int asg_spmm_csr_split(const int64_t* crow, const int64_t* col, const float* val, const float* x, float* y,

@@ -204,7 +204,7 @@ class ShardedSpmm:
 
     def __init__(self, shard: RowShard, features: int, *, group=None, dtype=torch.float32, feature_tile: int = 128,
                  warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
-                 exchange: Optional[str] = None, copy_streams: int = 1) -> None:
+                 exchange: Optional[str] = None, copy_streams: int = 1, slabs: int = 0) -> None:
         self.shard = shard
         self.group = group
         self.features = features
@@ -227,6 +227,15 @@ class ShardedSpmm:
         self.exchange = "peer" if self.handle is not None else "nccl"
         if not shard.groups:
             shard.groups = [[k] for k in arrival_order(shard.rank, shard.world)]
+        # Feature-slab mode (peer exchange only): X is pulled in `slabs` bands of feature columns, band s
+        # of every remote shard before band s+1, and each band is multiplied over the WHOLE local CSR
+        # as soon as it is complete.  No column blocks, so rows keep their full degree and nothing is
+        # accumulated into Y twice; the price is that no product can start before the first band is in.
+        self.slabs = 0
+        if self.exchange == "peer" and slabs and slabs > 1 and features % (32 * slabs) == 0:
+            self.slabs = int(slabs)
+            self._whole = ColumnBlock(shard.rank, shard.crow, shard.col, shard.val)
+            self._slab_events = [torch.cuda.Event() for _ in range(self.slabs)]
         self._events = [torch.cuda.Event() for _ in range(shard.world)] if device.type == "cuda" else []
         self._opened = torch.cuda.Event() if device.type == "cuda" else None
 
@@ -294,6 +303,46 @@ class ShardedSpmm:
                 main.wait_event(self._events[owner])
         self.handle.barrier(channel=1)
 
+    def _start_slab_pulls(self) -> None:
+        """Slab mode, on the communication stream: barrier, then band after band of feature columns
+        from every source (pitched copy-engine copies), an event after each band, barrier."""
+        shard = self.shard
+        main = self.comm_stream
+        width = self.features // self.slabs
+        self.handle.barrier(channel=0)
+        streams = [main] + self.copy_streams
+        if self.copy_streams:
+            self._opened.record(main)
+            for extra in self.copy_streams:
+                extra.wait_event(self._opened)
+        sources = arrival_order(shard.rank, shard.world)[1:]
+        for band in range(self.slabs):
+            for i, owner in enumerate(sources):
+                stream = streams[i % len(streams)]
+                with torch.cuda.stream(stream):
+                    _native.copy_columns(self._shard_view(owner), self._peers[owner], band * width, width)
+            for extra in self.copy_streams:  # the band is complete when every stream has finished its share
+                self._opened.record(extra)
+                main.wait_event(self._opened)
+            self._slab_events[band].record(main)
+        self.handle.barrier(channel=1)
+
+    def _slab_products(self, y: torch.Tensor, current) -> None:
+        """One SpMM per band over the whole local CSR; with ``current`` given, each waits for its band."""
+        width = self.features // self.slabs
+        tile = min(self.feature_tile, width)
+        block = self._whole
+        if block.workspace is None:
+            block.workspace = torch.empty(_native.workspace_bytes(y.size(0)), dtype=torch.uint8, device=y.device)
+            block.plan_ready = False
+        for band in range(self.slabs):
+            if current is not None:
+                current.wait_event(self._slab_events[band])
+            _native.spmm_range(block.crow, block.col, block.val, self.x_full, y, feature_begin=band * width,
+                               feature_count=width, feature_tile=tile, warps=self.warps, threshold=self.threshold,
+                               flags=_native.FLAG_PLAN_READY if block.plan_ready else 0, workspace=block.workspace)
+            block.plan_ready = True
+
     def exchange_only(self) -> None:
         """Runs just the gather of X (for measurements); the current stream waits for its end."""
         if self.shard.world == 1:
@@ -302,7 +351,10 @@ class ShardedSpmm:
             current = torch.cuda.current_stream(self.device)
             self.comm_stream.wait_stream(current)
             with torch.cuda.stream(self.comm_stream):
-                self._start_pulls()
+                if self.slabs:
+                    self._start_slab_pulls()
+                else:
+                    self._start_pulls()
             current.wait_stream(self.comm_stream)
             return
         for _, works in self._start_exchange():
@@ -317,6 +369,17 @@ class ShardedSpmm:
         kw = dict(feature_tile=self.feature_tile, warps=self.warps, threshold=self.threshold)
         if shard.world == 1:
             _block_spmm(shard.blocks[0], self.x_full, y, False, **kw)
+            return y
+
+        if self.exchange == "peer" and self.slabs:
+            current = torch.cuda.current_stream(self.device)
+            self.comm_stream.wait_stream(current)
+            with torch.cuda.stream(self.comm_stream):
+                self._start_slab_pulls()
+            if not overlap:
+                current.wait_stream(self.comm_stream)
+            self._slab_products(y, current if overlap else None)
+            current.wait_stream(self.comm_stream)
             return y
 
         if self.exchange == "peer":
@@ -364,11 +427,11 @@ class ShardedAutoSAGEConv(torch.nn.Module):
 
     def __init__(self, shard: RowShard, in_channels: int, out_channels: int, *, bias: bool = True, group=None,
                  feature_tile: int = 128, warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
-                 exchange: Optional[str] = None, copy_streams: int = 1) -> None:
+                 exchange: Optional[str] = None, copy_streams: int = 1, slabs: int = 0) -> None:
         super().__init__()
         self.linear = torch.nn.Linear(in_channels, out_channels, bias=bias)
         self.spmm = ShardedSpmm(shard, in_channels, group=group, feature_tile=feature_tile, warps=warps,
-                                threshold=threshold, exchange=exchange, copy_streams=copy_streams)
+                                threshold=threshold, exchange=exchange, copy_streams=copy_streams, slabs=slabs)
 
     def forward(self, x_local: Optional[torch.Tensor] = None, overlap: bool = True) -> torch.Tensor:
         if x_local is not None and x_local.data_ptr() != self.spmm.x_local.data_ptr():

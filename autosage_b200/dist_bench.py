@@ -86,7 +86,7 @@ def run(args):
     torch.manual_seed(0)
     layer = asg_dist.ShardedAutoSAGEConv(shard, f, out_f, bias=True, feature_tile=args.tile, warps=args.warps,
                                          threshold=args.hub_threshold, exchange=args.exchange,
-                                         copy_streams=args.copy_streams).to(device)
+                                         copy_streams=args.copy_streams, slabs=args.slabs).to(device)
     torch.nn.init.xavier_uniform_(layer.linear.weight)
     torch.nn.init.zeros_(layer.linear.bias)
     gen = torch.Generator(device=device).manual_seed(3)
@@ -138,6 +138,9 @@ def run(args):
         layer.spmm.exchange_only()
 
     def compute_only():
+        if layer.spmm.slabs:
+            layer.spmm._slab_products(aggregated_scratch, None)
+            return
         kw = dict(feature_tile=args.tile, warps=args.warps, threshold=args.hub_threshold)
         for g, block in enumerate(shard.blocks):
             asg_dist._block_spmm(block, layer.spmm.x_full, aggregated_scratch, g > 0, **kw)
@@ -204,6 +207,7 @@ def run(args):
                                f"({'copy-engine pulls from peer memory' if layer.spmm.exchange == 'peer' else 'NCCL send/recv steps'}), "
                                f"overlapped with {len(shard.blocks)} column-block SpMMs per GPU",
                 "exchange": layer.spmm.exchange,
+                "feature_slabs": layer.spmm.slabs,
                 "kernel_parameters": {"feature_tile": args.tile, "warps_per_block": args.warps,
                                       "hub_threshold": args.hub_threshold},
                 "l2": "per-GPU inputs per step (CSR shard + gathered X) exceed the 126 MB L2; no explicit flush",

@@ -377,8 +377,9 @@ def run_ours_single(args) -> dict:
             "d2h_bytes_per_step": d2h_bytes,
             "inputs": "CSR arrays resident on the device; dense operands (and edge weights) copied every step",
         },
-        # SpMM and SDDMM launch two kernels per step (main queues + the short-row queue), attention one
-        "gpu_launches": args.steps * (1 if args.workload == "c4_attention" else 2),
+        # every operator launches two kernels per step: the main queues and the short-row queue
+        # (SDDMM with a key matrix above 64 MB: one main launch per 64-feature pass)
+        "gpu_launches": args.steps * (2 + (f // 64 - 1 if args.workload == "c3_sddmm" and f >= 128 and n * f * 4 > (64 << 20) else 0)),
         "clocks": clocks.summary(),
     }
 
@@ -505,6 +506,7 @@ def main() -> None:
     parser.add_argument("--cpu-sample-nnz", type=int, default=4_000_000)
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--groups", type=int, default=None, help="column groups per GPU in the sharded path")
+    parser.add_argument("--slabs", type=int, default=0, help="feature bands of the slab exchange (sharded path; 0 = column blocks)")
     parser.add_argument("--copy-streams", type=int, default=1, help="streams used for the peer pulls (sharded path)")
     parser.add_argument("--exchange", default=None, choices=["peer", "nccl"], help="how X is gathered (sharded path)")
     args = parser.parse_args()

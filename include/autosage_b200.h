@@ -107,6 +107,18 @@ int asg_spmm_csr_ex(const int64_t* crow, const int64_t* col, const float* val, c
                     int warps_per_block, int64_t hub_threshold, unsigned flags, void* workspace,
                     size_t workspace_bytes, void* stream);
 
+/*
+ * As asg_spmm_csr_ex, but only the output columns [feature_begin, feature_begin + feature_count) are
+ * computed (x and y keep their leading dimension f).  The range must start on a feature_tile boundary
+ * and end on one or at f.  Used by the sharded path, which multiplies a band of feature columns as
+ * soon as that band of every remote shard has arrived.  No counterpart in the reference.
+ */
+int asg_spmm_csr_range(const int64_t* crow, const int64_t* col, const float* val, const float* x,
+                       float* y, int64_t n_rows, int64_t nnz, int64_t f, int64_t feature_begin,
+                       int64_t feature_count, int feature_tile, int warps_per_block,
+                       int64_t hub_threshold, unsigned flags, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
 /* out[nnz]: out[e] = <q[row(e), :], k[col[e], :]>  (reference op autosage::sddmm_csr). */
 int asg_sddmm_csr(const int64_t* crow, const int64_t* col, const float* q, const float* k,
                   float* out, int64_t n_rows, int64_t nnz, int64_t f, void* workspace,
@@ -147,6 +159,13 @@ int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, c
  * (autosage/conv.py:55), issued after a plain matrix product.
  */
 int asg_add_row_bias(float* out, const float* bias, int64_t rows, int64_t cols, void* stream);
+
+/*
+ * Pitched device-to-device copy of `height` rows of `width_bytes` bytes (cudaMemcpy2DAsync; runs on
+ * the copy engines).  Either pointer may be peer-mapped memory of another GPU.
+ */
+int asg_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                size_t height, void* stream);
 
 /*
  * Status word written by kernels whose bounded waits gave up (0 = none).  The word lives in the

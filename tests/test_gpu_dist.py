@@ -1,0 +1,81 @@
+"""Row-partitioned path on real GPUs (needs at least two; skipped otherwise): every exchange mode
+must reproduce the single-GPU / oracle result."""
+from __future__ import annotations
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from helpers import dense, random_csr, to_np, weights
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, out_dir: str):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    device = torch.device("cuda", rank)
+    torch.cuda.set_device(device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from autosage_b200 import dist as asg_dist
+
+        crow, col = random_csr(6000, 14, seed=21, hubs={7: 5000, 3500: 1200})
+        val = weights(col.numel(), 4)
+        x = dense(6000, 128, 5)
+        bounds = asg_dist.partition_rows(crow, world)
+        results = {}
+        for name, kwargs, groups in (("peer_blocks", dict(exchange="peer"), None),
+                                     ("peer_blocks_2streams", dict(exchange="peer", copy_streams=2), 1),
+                                     ("peer_slabs2", dict(exchange="peer", slabs=2), 1),
+                                     ("peer_slabs4", dict(exchange="peer", slabs=4, copy_streams=2), 1),
+                                     ("nccl_blocks", dict(exchange="nccl"), None)):
+            shard = asg_dist.shard_csr(crow, col, val, rank, world, bounds, device=device, groups=groups)
+            torch.manual_seed(0)
+            layer = asg_dist.ShardedAutoSAGEConv(shard, 128, 16, feature_tile=64, warps=4, threshold=1024,
+                                                 **kwargs).to(device)
+            layer.spmm.x_full.fill_(float("nan"))
+            local = x[shard.row_begin:shard.row_end].to(device)
+            with torch.no_grad():
+                for _ in range(2):                      # twice: buffers and plans are reused
+                    out = layer(local)
+                agg = layer.spmm.forward()
+            results[name] = {"agg": agg.cpu(), "out": out.cpu(), "mode": layer.spmm.exchange,
+                             "slabs": layer.spmm.slabs}
+            dist.barrier()
+        torch.save({"results": results, "begin": int(bounds[rank]), "end": int(bounds[rank + 1])},
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_layer_on_gpus(tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    from oracle import oracle as orc
+
+    world = min(torch.cuda.device_count(), 4)
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    crow, col = random_csr(6000, 14, seed=21, hubs={7: 5000, 3500: 1200})
+    val = weights(col.numel(), 4)
+    x = dense(6000, 128, 5)
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    parts = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    for name in parts[0]["results"]:
+        agg = torch.cat([p["results"][name]["agg"] for p in parts]).numpy()
+        ok, ratio = orc.within_tolerance(agg, exact, to_np(crow))
+        assert ok, (name, ratio)
+    assert parts[0]["results"]["peer_slabs2"]["slabs"] in (0, 2)   # 0 only if symmetric memory was unavailable

@@ -431,3 +431,33 @@ def test_sddmm_feature_passes_on_a_large_key_matrix(lib, orc):
         ok, ratio = orc.within_tolerance(out.cpu().numpy(), exact, to_np(crow), per_edge=True, rtol=RTOL, atol=ATOL)
         assert ok, f"worst error/bound {ratio:.3f}"
     assert not torch.isnan(tiled).any()
+
+
+def test_spmm_feature_range(lib, orc):
+    """Only a band of output columns is computed; the rest of y is left untouched."""
+    crow, col = random_csr(500, 12, seed=3, hubs={4: 2000})
+    x = dense(500, 192, 1)
+    val = weights(col.numel(), 2)
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    dev = torch.device("cuda")
+    crow_d, col_d, val_d, x_d = crow.to(dev), col.to(dev), val.to(dev), x.to(dev)
+    ws = torch.empty(lib.workspace_bytes(500), dtype=torch.uint8, device=dev)
+    y = torch.full((500, 192), float("nan"), device=dev)
+    for begin, count, tile in ((64, 64, 64), (0, 64, 32), (128, 64, 64)):
+        lib.spmm_range(crow_d, col_d, val_d, x_d, y, feature_begin=begin, feature_count=count, feature_tile=tile,
+                       warps=4, threshold=256, flags=0, workspace=ws)
+    torch.cuda.synchronize()
+    assert_close(orc, y, exact, crow)
+    y2 = torch.full((500, 192), float("nan"), device=dev)
+    lib.spmm_range(crow_d, col_d, val_d, x_d, y2, feature_begin=128, feature_count=64, feature_tile=64, warps=4,
+                   threshold=256, flags=0, workspace=ws)
+    torch.cuda.synchronize()
+    assert bool(torch.isnan(y2[:, :128]).all()) and not bool(torch.isnan(y2[:, 128:]).any())
+    with pytest.raises(RuntimeError, match="feature_tile boundary"):
+        lib.spmm_range(crow_d, col_d, val_d, x_d, y2, feature_begin=32, feature_count=64, feature_tile=64, warps=4,
+                       threshold=256, flags=0, workspace=ws)
+    # pitched copy of a band of columns
+    dst = torch.zeros(500, 192, device=dev)
+    lib.copy_columns(dst, x_d, 64, 32)
+    torch.cuda.synchronize()
+    assert torch.equal(dst[:, 64:96], x_d[:, 64:96]) and float(dst[:, :64].abs().sum()) == 0.0
