@@ -48,6 +48,7 @@ SIGNATURES = {
     "asg_csr_row_softmax": (_INT, [_P, _P, _P, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_csr_attention": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _F32, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_add_row_bias": (_INT, [_P, _P, _I64, _I64, _P]),
+    "asg_linear_bias": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "asg_copy_2d": (_INT, [_P, _SZ, _P, _SZ, _SZ, _SZ, _P]),
     "asg_workspace_status": (_INT, [_P, _P, _P]),
     "asg_spmm_csr_split_noalloc": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _P]),
@@ -260,6 +261,12 @@ def attention(crow, col, query, key, value, out, *, scale: float, warps: int, th
 def add_row_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
     """out[r, :] += bias, in place (contiguous float32 CUDA tensors)."""
     check(library().asg_add_row_bias(out.data_ptr(), bias.data_ptr(), out.size(0), out.size(1), _stream(out.device)))
+
+
+def linear_bias(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out = x @ weight^T + bias on the tensor cores at float32 accuracy (contiguous float32 CUDA tensors)."""
+    check(library().asg_linear_bias(x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(),
+                                    out.data_ptr(), x.size(0), x.size(1), weight.size(0), _stream(x.device)))
 
 
 def workspace_status(workspace: torch.Tensor) -> int:

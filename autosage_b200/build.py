@@ -42,6 +42,28 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc was not found; it is required to build libautosage_b200.so")
 
 
+def cutlass_include_dirs() -> list[Path]:
+    """The CUTLASS/CuTe header tree (headers only) that asg_linear.cu instantiates its GEMM from.
+    Looked up in CUTLASS_INCLUDE_DIR, then in the trees that Python packages of this environment
+    vendor (flashinfer, tilelang)."""
+    import importlib.util
+
+    candidates = []
+    if os.environ.get("CUTLASS_INCLUDE_DIR"):
+        candidates.append(Path(os.environ["CUTLASS_INCLUDE_DIR"]))
+    for package, relative in (("flashinfer", "data/cutlass/include"), ("tilelang", "3rdparty/cutlass/include")):
+        try:
+            spec = importlib.util.find_spec(package)
+        except (ImportError, ValueError):
+            spec = None
+        if spec is not None and spec.submodule_search_locations:
+            candidates.append(Path(list(spec.submodule_search_locations)[0]) / relative)
+    for candidate in candidates:
+        if (candidate / "cutlass" / "gemm" / "collective" / "sm100_mma_warpspecialized_emulated.hpp").is_file():
+            return [candidate]
+    raise RuntimeError("no CUTLASS header tree with the sm_100 collectives was found; set CUTLASS_INCLUDE_DIR")
+
+
 def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
@@ -68,6 +90,7 @@ def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | N
         return target
     nvcc = _nvcc()
     flags = list(NVCC_FLAGS) + [f"-I{INCLUDE}", f"-I{CSRC}"] + list(extra_flags or [])
+    flags += [f"-I{d}" for d in cutlass_include_dirs()] + ["-diag-suppress", "20012"]
     if verbose:
         flags += ["-Xptxas", "-v"]
     obj_dir = LIB_DIR / ("obj" if output is None else f"obj_{target.stem}")
@@ -77,6 +100,8 @@ def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | N
     for src in srcs:
         obj = obj_dir / (src.stem + ".o")
         objects.append(obj)
+        if not force and not extra_flags and not _stale(obj, [src] + headers + [Path(__file__)]):
+            continue
         cmd = [nvcc, *flags, "-c", str(src), "-o", str(obj)]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False

@@ -327,8 +327,9 @@ class ShardedSpmm:
             self._slab_events[band].record(main)
         self.handle.barrier(channel=1)
 
-    def _slab_products(self, y: torch.Tensor, current) -> None:
-        """One SpMM per band over the whole local CSR; with ``current`` given, each waits for its band."""
+    def _slab_products(self, y: torch.Tensor, current, after_band=None) -> None:
+        """One SpMM per band over the whole local CSR; with ``current`` given, each waits for its band.
+        ``after_band(band, first_column, width)`` runs after each band's product is enqueued."""
         width = self.features // self.slabs
         tile = min(self.feature_tile, width)
         block = self._whole
@@ -342,6 +343,8 @@ class ShardedSpmm:
                                feature_count=width, feature_tile=tile, warps=self.warps, threshold=self.threshold,
                                flags=_native.FLAG_PLAN_READY if block.plan_ready else 0, workspace=block.workspace)
             block.plan_ready = True
+            if after_band is not None:
+                after_band(band, band * width, width)
 
     def exchange_only(self) -> None:
         """Runs just the gather of X (for measurements); the current stream waits for its end."""
@@ -361,8 +364,13 @@ class ShardedSpmm:
             for work in works:
                 work.wait()
 
-    def forward(self, out: Optional[torch.Tensor] = None, overlap: bool = True) -> torch.Tensor:
-        """y_local = A_local @ gather(X).  ``x_local`` must already hold this rank's features."""
+    def forward(self, out: Optional[torch.Tensor] = None, overlap: bool = True, *, before_products=None,
+                after_band=None) -> torch.Tensor:
+        """y_local = A_local @ gather(X).  ``x_local`` must already hold this rank's features.
+
+        Slab mode only: ``before_products()`` runs on the current stream once the pulls are enqueued,
+        ``after_band(band, first_column, width)`` after each band's product (the layer uses them to
+        run its Linear band by band, under the transfer of the following band)."""
         shard = self.shard
         y = out if out is not None else torch.empty(shard.n_local, self.features, dtype=self.x_full.dtype,
                                                     device=self.device)
@@ -378,7 +386,9 @@ class ShardedSpmm:
                 self._start_slab_pulls()
             if not overlap:
                 current.wait_stream(self.comm_stream)
-            self._slab_products(y, current if overlap else None)
+            if before_products is not None:
+                before_products()
+            self._slab_products(y, current if overlap else None, after_band)
             current.wait_stream(self.comm_stream)
             return y
 
@@ -436,5 +446,28 @@ class ShardedAutoSAGEConv(torch.nn.Module):
     def forward(self, x_local: Optional[torch.Tensor] = None, overlap: bool = True) -> torch.Tensor:
         if x_local is not None and x_local.data_ptr() != self.spmm.x_local.data_ptr():
             self.spmm.x_local.copy_(x_local)
-        aggregated = self.spmm.forward(overlap=overlap)
-        return apply_linear(self.linear, aggregated)
+        spmm = self.spmm
+        differentiating = torch.is_grad_enabled() and any(p.requires_grad for p in self.linear.parameters())
+        if not spmm.slabs or spmm.shard.world == 1 or differentiating:
+            return apply_linear(self.linear, spmm.forward(overlap=overlap))
+        # Slab mode: out = bias + sum over bands of Y[:, band] @ W[:, band]^T.  The partial product of
+        # band s runs while band s+1 is still crossing NVLink, so only the last band's SpMM and its
+        # partial GEMM remain after the transfer.
+        linear = self.linear
+        out = torch.empty(spmm.shard.n_local, linear.out_features, dtype=spmm.x_full.dtype, device=spmm.device)
+        y = torch.empty(spmm.shard.n_local, spmm.features, dtype=spmm.x_full.dtype, device=spmm.device)
+        weight_t = linear.weight.t()
+
+        def before_products():
+            if linear.bias is not None:
+                out.copy_(linear.bias.expand_as(out))
+
+        def after_band(band, first, width):
+            part, w = y[:, first:first + width], weight_t[first:first + width]
+            if band == 0 and linear.bias is None:
+                torch.mm(part, w, out=out)
+            else:
+                out.addmm_(part, w)
+
+        spmm.forward(out=y, overlap=overlap, before_products=before_products, after_band=after_band)
+        return out

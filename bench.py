@@ -5,11 +5,14 @@
 
 One "step" is one pass of the hot path (one SpMM / SDDMM / attention call) over the whole synthetic
 graph.  Metric: algorithmic GB/s (bytes = CSR + gathered dense rows + output, the byte model of the
-roofline) with edges*F/s alongside.  N = 1 runs BASELINE configuration 2 (232,965 rows, ~114.6 M
-nnz, weighted, F = 128); N > 1 runs the row-partitioned AutoSAGEConv forward of configuration 5
-(2,449,029 rows, ~123.7 M nnz, Linear F->256): rows sharded by nnz over the ranks, X gathered over
-NVLink inside the timed region (peer-memory pulls, or NCCL send/recv with --exchange nccl), strong
-scaling; each such line also carries the same layer timed on one GPU (single_gpu_ms_per_step).
+roofline) with edges*F/s alongside.  The default workload at every N is the AutoSAGEConv forward of
+BASELINE configuration 5 (2,449,029 rows, ~123.7 M nnz, F = 128, Linear F->256), the configuration the
+1/2/4/8-GPU series is quoted on: at N = 1 the whole graph on one GPU, at N > 1 rows sharded by nnz over
+the ranks with X gathered over NVLink inside the timed region (peer-memory pulls, or NCCL send/recv
+with --exchange nccl); strong scaling, and each multi-GPU line also carries the same layer timed on
+one GPU in the same job (single_gpu_ms_per_step).  The N = 1 line adds short runs of configurations 2
+(SpMM, 232,965 rows, ~114.6 M nnz, weighted), 3 (SDDMM) and 4 (fused attention) under other_configs;
+--workload selects any of them as the headline instead.
 
 The line printed by rank 0 carries, beside the contract keys:
   roofline      achieved algorithmic GB/s of the dominant kernel against the measured HBM copy peak
@@ -43,6 +46,7 @@ FALLBACK_HBM_GBS = 6650.0
 # of the byte counters report null.
 NCU_DRAM_TRAFFIC = {
     ("c2_spmm", 128, 64): (6.04e9, "profiles/spmm_kernel_c2_f128.md"),
+    ("c5_spmm", 128, 128): (60.19e9, "profiles/spmm_kernel_c5_f128.md"),
 }
 
 
@@ -505,6 +509,8 @@ def main() -> None:
     parser.add_argument("--hub-threshold", type=int, default=1024)
     parser.add_argument("--cpu-sample-nnz", type=int, default=4_000_000)
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-other-configs", action="store_true",
+                        help="N = 1: skip the short runs of configurations 2, 3 and 4")
     parser.add_argument("--groups", type=int, default=None, help="column groups per GPU in the sharded path")
     parser.add_argument("--slabs", type=int, default=0, help="feature bands of the slab exchange (sharded path; 0 = column blocks)")
     parser.add_argument("--copy-streams", type=int, default=1, help="streams used for the peer pulls (sharded path)")
@@ -513,7 +519,7 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if args.workload is None:
-        args.workload = "c2_spmm" if max(args.gpus, world) == 1 else "c5_conv"
+        args.workload = "c5_conv"
     if args.tile is None:
         # X of configuration 2 is about the size of L2: 64-wide tiles keep the gathered slice
         # resident; configuration 5's X is ten times L2 and whole 128-float rows stream best.

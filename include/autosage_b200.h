@@ -161,6 +161,16 @@ int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, c
 int asg_add_row_bias(float* out, const float* bias, int64_t rows, int64_t cols, void* stream);
 
 /*
+ * out[rows, out_features] = x[rows, in_features] @ weight[out_features, in_features]^T + bias:
+ * the layer's nn.Linear (autosage/conv.py:55) at float32 accuracy on the tensor cores (each float32
+ * operand is split into three bfloat16 pieces, the piece products are summed in float32; no TF32
+ * rounding of the inputs).  bias may be null.  in_features and out_features must be multiples
+ * of 4 and all pointers 16-byte aligned; x, weight and out are dense row-major.
+ */
+int asg_linear_bias(const float* x, const float* weight, const float* bias, float* out, int64_t rows,
+                    int64_t in_features, int64_t out_features, void* stream);
+
+/*
  * Pitched device-to-device copy of `height` rows of `width_bytes` bytes (cudaMemcpy2DAsync; runs on
  * the copy engines).  Either pointer may be peer-mapped memory of another GPU.
  */

@@ -74,8 +74,14 @@ def test_sharded_layer_on_gpus(tmp_path):
     x = dense(6000, 128, 5)
     exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
     parts = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    torch.manual_seed(0)
+    linear = torch.nn.Linear(128, 16)       # the layers above draw their weights from the same seed
+    expected_out = exact @ linear.weight.detach().double().numpy().T + linear.bias.detach().double().numpy()
     for name in parts[0]["results"]:
         agg = torch.cat([p["results"][name]["agg"] for p in parts]).numpy()
         ok, ratio = orc.within_tolerance(agg, exact, to_np(crow))
         assert ok, (name, ratio)
+        out = torch.cat([p["results"][name]["out"] for p in parts]).double().numpy()
+        scale = np.abs(expected_out).max()
+        assert np.abs(out - expected_out).max() <= 2e-5 * scale, name
     assert parts[0]["results"]["peer_slabs2"]["slabs"] in (0, 2)   # 0 only if symmetric memory was unavailable

@@ -461,3 +461,52 @@ def test_spmm_feature_range(lib, orc):
     lib.copy_columns(dst, x_d, 64, 32)
     torch.cuda.synchronize()
     assert torch.equal(dst[:, 64:96], x_d[:, 64:96]) and float(dst[:, :64].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("rows,k,n,with_bias", [(1, 128, 256, True), (127, 128, 256, True), (129, 64, 16, True),
+                                                 (1000, 100, 36, False), (5000, 256, 256, True), (0, 128, 256, True)])
+def test_linear_bias_matches_float64(lib, rows, k, n, with_bias):
+    """The tensor-core Linear keeps float32 accuracy (rtol 1e-5, atol 1e-5 * sqrt(in_features) against float64)."""
+    dev = torch.device("cuda")
+    gen = torch.Generator().manual_seed(rows * 7 + k)
+    x = torch.randn(rows, k, generator=gen).to(dev)
+    weight = (torch.randn(n, k, generator=gen) / k ** 0.5).to(dev)
+    bias = torch.randn(n, generator=gen).to(dev) if with_bias else None
+    out = torch.full((rows, n), float("nan"), device=dev)
+    lib.linear_bias(x, weight, bias, out)
+    torch.cuda.synchronize()
+    exact = x.double() @ weight.double().t()
+    if with_bias:
+        exact = exact + bias.double()
+    if rows:
+        err = (out.double() - exact).abs()
+        bound = 1e-5 * exact.abs() + 1e-5 * k ** 0.5
+        assert bool((err <= bound).all()), float((err / bound).max())
+        # at least as close to float64 as the float32 library product
+        library = torch.mm(x, weight.t()) + (bias if with_bias else 0)
+        assert float(err.max()) <= 2.0 * float((library.double() - exact).abs().max()) + 1e-7
+
+
+def test_linear_bias_rejects_unaligned_sizes(lib):
+    dev = torch.device("cuda")
+    x, weight, out = torch.zeros(8, 6, device=dev), torch.zeros(4, 6, device=dev), torch.zeros(8, 4, device=dev)
+    with pytest.raises(RuntimeError, match="multiples of 4"):
+        lib.linear_bias(x, weight, None, out)
+
+
+def test_layer_linear_uses_tensor_core_path(lib, monkeypatch):
+    """apply_linear: same result through the tensor-core route and the cuBLAS route."""
+    from autosage_b200 import conv
+
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    linear = torch.nn.Linear(128, 256).to(dev)
+    x = dense(3000, 128, 9).to(dev)
+    with torch.no_grad():
+        fast = conv.apply_linear(linear, x)
+        monkeypatch.setenv("AUTOSAGE_LINEAR", "cublas")
+        plain = conv.apply_linear(linear, x)
+    assert torch.allclose(fast, plain, rtol=1e-5, atol=1e-5 * 128 ** 0.5)
+    y = conv.apply_linear(linear, x.requires_grad_())          # gradient wanted: differentiable route
+    y.sum().backward()
+    assert x.grad is not None and linear.weight.grad is not None
