@@ -238,6 +238,26 @@ class ShardedSpmm:
             self._slab_events = [torch.cuda.Event() for _ in range(self.slabs)]
         self._events = [torch.cuda.Event() for _ in range(shard.world)] if device.type == "cuda" else []
         self._opened = torch.cuda.Event() if device.type == "cuda" else None
+        # Optional timeline: set ``trace`` to a list and every forward appends {name: timing event};
+        # ``timeline_ms`` turns the collected steps into mean offsets from the step's start.
+        self.trace: Optional[list] = None
+        self._marks: Optional[dict] = None
+
+    def _mark(self, name: str, stream=None) -> None:
+        if self._marks is not None:
+            event = torch.cuda.Event(enable_timing=True)
+            event.record(stream if stream is not None else torch.cuda.current_stream(self.device))
+            self._marks[name] = event
+
+    def timeline_ms(self) -> dict:
+        """Mean offset (ms) of every recorded mark from "start", over the traced steps (synchronises)."""
+        torch.cuda.synchronize(self.device)
+        sums: dict = {}
+        for marks in self.trace or []:
+            for name, event in marks.items():
+                if name != "start":
+                    sums.setdefault(name, []).append(marks["start"].elapsed_time(event))
+        return {name: round(sum(v) / len(v), 4) for name, v in sums.items()}
 
     def _try_symmetric(self, dtype) -> None:
         """Allocate X in symmetric memory and map the peers' copies; all ranks agree on the outcome."""
@@ -287,6 +307,7 @@ class ShardedSpmm:
         shard = self.shard
         main = self.comm_stream
         self.handle.barrier(channel=0)
+        self._mark("pulls_begin", main)
         streams = [main] + self.copy_streams
         if self.copy_streams:
             self._opened.record(main)
@@ -301,7 +322,9 @@ class ShardedSpmm:
         if self.copy_streams:
             for owner in sources:
                 main.wait_event(self._events[owner])
+        self._mark("pulls_end", main)
         self.handle.barrier(channel=1)
+        self._mark("closing_barrier", main)
 
     def _start_slab_pulls(self) -> None:
         """Slab mode, on the communication stream: barrier, then band after band of feature columns
@@ -375,8 +398,13 @@ class ShardedSpmm:
         y = out if out is not None else torch.empty(shard.n_local, self.features, dtype=self.x_full.dtype,
                                                     device=self.device)
         kw = dict(feature_tile=self.feature_tile, warps=self.warps, threshold=self.threshold)
+        self._marks = {} if self.trace is not None else None
+        if self._marks is not None:
+            self.trace.append(self._marks)
+        self._mark("start")
         if shard.world == 1:
             _block_spmm(shard.blocks[0], self.x_full, y, False, **kw)
+            self._mark("spmm_end")
             return y
 
         if self.exchange == "peer" and self.slabs:
@@ -405,6 +433,7 @@ class ShardedSpmm:
                         if member != shard.rank:
                             current.wait_event(self._events[member])
                 _block_spmm(block, self.x_full, y, g > 0, **kw)
+                self._mark(f"block{g}_end")
             # the closing barrier of the exchange must be part of this step's stream order
             current.wait_stream(self.comm_stream)
             return y
@@ -449,7 +478,9 @@ class ShardedAutoSAGEConv(torch.nn.Module):
         spmm = self.spmm
         differentiating = torch.is_grad_enabled() and any(p.requires_grad for p in self.linear.parameters())
         if not spmm.slabs or spmm.shard.world == 1 or differentiating:
-            return apply_linear(self.linear, spmm.forward(overlap=overlap))
+            out = apply_linear(self.linear, spmm.forward(overlap=overlap))
+            spmm._mark("linear_end")
+            return out
         # Slab mode: out = bias + sum over bands of Y[:, band] @ W[:, band]^T.  The partial product of
         # band s runs while band s+1 is still crossing NVLink, so only the last band's SpMM and its
         # partial GEMM remain after the transfer.

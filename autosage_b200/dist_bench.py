@@ -215,6 +215,23 @@ def run(args):
         for g, block in enumerate(shard.blocks):
             asg_dist._block_spmm(block, layer.spmm.x_full, aggregated_scratch, g > 0, **kw)
 
+    # timeline of a few more (untimed) steps: mean offsets of the exchange and compute marks from the
+    # step's start on this rank, events recorded in the streams the work runs on
+    timeline = None
+    if multi:
+        layer.spmm.trace = []
+        for _ in range(5):
+            step()
+        own = layer.spmm.timeline_ms()
+        layer.spmm.trace = None
+        names = sorted(own)
+        mine = torch.tensor([own[name] for name in names], device=device)
+        everyone = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        stacked = torch.stack(everyone).cpu()
+        order = sorted(range(len(names)), key=lambda i: float(stacked[:, i].max()))
+        timeline = {names[i]: [round(float(stacked[:, i].min()), 3), round(float(stacked[:, i].max()), 3)] for i in order}
+
     aggregated_scratch = torch.empty(shard.n_local, f, device=device)
     with torch.no_grad():
         breakdown = {
@@ -321,6 +338,8 @@ def run(args):
             "algorithmic_bytes_per_step": algorithmic,
             "nvlink_receive_bytes_per_gpu": 4 * (n - shard.n_local) * f,
             "breakdown_ms": breakdown,
+            # [earliest rank, latest rank] offset of each mark from its rank's step start
+            "timeline_ms_min_max_over_ranks": timeline,
             "single_gpu_ms_per_step": None if single_ms is None else round(single_ms, 4),
             "speedup_vs_1gpu_same_workload": None if single_ms is None else round(single_ms / ms_per_step, 3),
             "roofline": roofline,
