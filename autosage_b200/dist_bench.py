@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import os
 import statistics
+import time
 
 import torch
 import torch.distributed as dist
@@ -155,9 +156,13 @@ def run(args):
 
     stream = torch.cuda.current_stream()
     spmm_events: list[tuple] = []
+    # multi-GPU: the whole step (pulls, barriers, column-block SpMMs, Linear) replayed as one CUDA graph
+    replay = layer.capture() if multi and not args.no_graph else None
 
     def step():
         with torch.no_grad():
+            if replay is not None:
+                return replay()
             if multi:
                 return layer()
             # one GPU: the layer's two stages written out, with events around the aggregation so that
@@ -177,10 +182,12 @@ def run(args):
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with bench.ClockSampler(local_rank) as clocks:
+        host_begin = time.perf_counter()
         begin.record(stream)
         for _ in range(args.steps):
             step()
         end.record(stream)
+        host_enqueue_ms = (time.perf_counter() - host_begin) * 1e3 / args.steps
         torch.cuda.synchronize()
         barrier()
         torch.cuda.synchronize()
@@ -220,8 +227,10 @@ def run(args):
     timeline = None
     if multi:
         layer.spmm.trace = []
-        for _ in range(5):
-            step()
+        with torch.no_grad():
+            for _ in range(6):
+                layer()  # eager on purpose: the marks are events recorded between the launches
+        layer.spmm.trace = layer.spmm.trace[1:]  # the first traced step starts with the ranks out of step
         own = layer.spmm.timeline_ms()
         layer.spmm.trace = None
         names = sorted(own)
@@ -241,25 +250,57 @@ def run(args):
         }
     del aggregated_scratch
 
-    # end to end: X shard from pinned host memory in, output shard back to the host, every step
-    out_host = torch.empty(shard.n_local, out_f).pin_memory()
+    # end to end: X shard from pinned host memory in, output shard back to the host, every step.
+    # Serial form: copy in, layer, copy out, one after the other on one stream.  Streamed form (the
+    # one reported as e2e): the copy-out of step i runs on a second stream into one of two host buffers
+    # while step i+1 copies in and computes - PCIe is full duplex - and the timed region ends when the
+    # last output has reached the host.
+    out_hosts = [torch.empty(shard.n_local, out_f).pin_memory() for _ in range(2)]
+    out_host = out_hosts[0]
+    drain = torch.cuda.Stream(device=device)
 
-    def e2e_step():
+    def e2e_serial_step():
         layer.spmm.x_local.copy_(x_shard_host, non_blocking=True)
         out_host.copy_(step(), non_blocking=True)
 
-    e2e_step()
-    torch.cuda.synchronize()
-    barrier()
+    # a replayed graph writes the same output buffer every step: stage it in one of two device
+    # buffers so that the copy-out of step i can still run under step i+1
+    staged = [torch.empty(shard.n_local, out_f, device=device) for _ in range(2)] if replay is not None else None
+    drained: list = [None, None]
+
+    def e2e_streamed_step(i):
+        layer.spmm.x_local.copy_(x_shard_host, non_blocking=True)
+        out = step()
+        if staged is not None:
+            if drained[i % 2] is not None:
+                stream.wait_event(drained[i % 2])
+            staged[i % 2].copy_(out)
+            out = staged[i % 2]
+        drain.wait_stream(stream)
+        with torch.cuda.stream(drain):
+            out_hosts[i % 2].copy_(out, non_blocking=True)
+            drained[i % 2] = torch.cuda.Event()
+            drained[i % 2].record(drain)
+        out.record_stream(drain)
+
     e2e_steps = max(2, min(args.steps, 5))
-    begin.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
-    end.record(stream)
-    torch.cuda.synchronize()
-    barrier()
-    e2e_elapsed = reduce_max(torch.tensor([begin.elapsed_time(end)], device=device))
-    e2e_ms = float(e2e_elapsed.item()) / e2e_steps
+
+    def time_e2e(run_steps):
+        run_steps(1)
+        stream.wait_stream(drain)
+        torch.cuda.synchronize()
+        barrier()
+        begin.record(stream)
+        run_steps(e2e_steps)
+        stream.wait_stream(drain)
+        end.record(stream)
+        torch.cuda.synchronize()
+        barrier()
+        took = reduce_max(torch.tensor([begin.elapsed_time(end)], device=device))
+        return float(took.item()) / e2e_steps
+
+    e2e_serial_ms = time_e2e(lambda k: [e2e_serial_step() for _ in range(k)])
+    e2e_ms = time_e2e(lambda k: [e2e_streamed_step(i) for i in range(k)])
     io_bytes = torch.tensor([x_shard_host.numel() * 4, out_host.numel() * 4], device=device, dtype=torch.long)
     local_nnz = torch.tensor([shard.col.numel()], device=device, dtype=torch.long)
     gathered = [torch.zeros_like(local_nnz) for _ in range(world)]
@@ -328,6 +369,7 @@ def run(args):
                                f"({'copy-engine pulls from peer memory' if layer.spmm.exchange == 'peer' else 'NCCL send/recv steps'}), "
                                f"overlapped with {len(shard.blocks)} column-block SpMMs per GPU",
                 "exchange": layer.spmm.exchange,
+                "cuda_graph": replay is not None,
                 "feature_slabs": layer.spmm.slabs,
                 "kernel_parameters": {"feature_tile": args.tile, "warps_per_block": args.warps,
                                       "hub_threshold": args.hub_threshold},
@@ -338,6 +380,7 @@ def run(args):
             "algorithmic_bytes_per_step": algorithmic,
             "nvlink_receive_bytes_per_gpu": 4 * (n - shard.n_local) * f,
             "breakdown_ms": breakdown,
+            "host_enqueue_ms_per_step": round(host_enqueue_ms, 4),
             # [earliest rank, latest rank] offset of each mark from its rank's step start
             "timeline_ms_min_max_over_ranks": timeline,
             "single_gpu_ms_per_step": None if single_ms is None else round(single_ms, 4),
@@ -350,6 +393,15 @@ def run(args):
                 "h2d_bytes_per_step": int(io_bytes[0].item()),
                 "d2h_bytes_per_step": int(io_bytes[1].item()),
                 "steps": e2e_steps,
+                "mode": "streamed: the copy-out of step i overlaps the copy-in and compute of step i+1 "
+                        "(second stream, two pinned output buffers); every step's input and output cross PCIe "
+                        "inside the timed region",
+            },
+            "e2e_serial": {
+                "value": round(algorithmic / (e2e_serial_ms * 1e-3) / 1e9, 2),
+                "unit": "GB/s",
+                "ms_per_step": round(e2e_serial_ms, 3),
+                "mode": "copy in, layer, copy out, strictly one after the other on one stream",
             },
             # per step and GPU: two SpMM kernels (main + short-row queue) for every column block (or
             # feature band), and the Linear kernel

@@ -48,6 +48,17 @@ def _require(condition: bool, message: str) -> None:
         raise RuntimeError(message)
 
 
+def _debug_check_columns(crow, col, bound: int) -> None:
+    """AUTOSAGE_CHECK_INDICES=1: verify the index arrays before a launch (synchronises; the reference
+    never checks ``col`` and an out-of-range entry there reads foreign memory)."""
+    if os.getenv("AUTOSAGE_CHECK_INDICES") != "1" or col.numel() == 0:
+        return
+    low, high = int(col.min().item()), int(col.max().item())
+    _require(low >= 0 and high < bound, f"col entries must lie in [0, {bound}); found [{low}, {high}]")
+    _require(int(crow[0].item()) == 0 and int(crow[-1].item()) == col.numel(), "crow must run from 0 to nnz")
+    _require(bool((crow[1:] >= crow[:-1]).all().item()), "crow must be non-decreasing")
+
+
 def _check_spmm_inputs(crow, col, val, x) -> None:
     _require(crow.is_cuda and col.is_cuda and x.is_cuda, "crow, col, and x must be CUDA tensors")
     _require(crow.dtype == torch.long and col.dtype == torch.long, "crow and col must use torch.long indices")
@@ -61,6 +72,7 @@ def _check_spmm_inputs(crow, col, val, x) -> None:
         _require(val.is_cuda and val.device == x.device, "val must be on the same CUDA device as x")
         _require(val.dtype == torch.float32 and val.is_contiguous(), "val must be contiguous float32")
         _require(val.numel() == col.numel(), "val must contain one weight per nonzero")
+    _debug_check_columns(crow, col, x.size(0))
 
 
 def _check_sddmm_inputs(crow, col, query, key) -> None:
@@ -74,6 +86,7 @@ def _check_sddmm_inputs(crow, col, query, key) -> None:
     _require(crow.is_contiguous() and col.is_contiguous() and query.is_contiguous() and key.is_contiguous(),
              "all SDDMM inputs must be contiguous")
     _require(query.size(0) <= 2**31 - 1 and query.size(1) <= 2**31 - 1, "SDDMM dimensions exceed the kernel index range")
+    _debug_check_columns(crow, col, key.size(0))
 
 
 def _op_spmm_csr(crow, col, val, x):

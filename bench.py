@@ -514,6 +514,8 @@ def main() -> None:
     parser.add_argument("--groups", type=int, default=None, help="column groups per GPU in the sharded path")
     parser.add_argument("--slabs", type=int, default=0, help="feature bands of the slab exchange (sharded path; 0 = column blocks)")
     parser.add_argument("--copy-streams", type=int, default=1, help="streams used for the peer pulls (sharded path)")
+    parser.add_argument("--no-graph", action="store_true",
+                        help="sharded path: launch every step eagerly instead of replaying a CUDA graph")
     parser.add_argument("--exchange", default=None, choices=["peer", "nccl"], help="how X is gathered (sharded path)")
     args = parser.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -54,6 +54,15 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
                 agg = layer.spmm.forward()
             results[name] = {"agg": agg.cpu(), "out": out.cpu(), "mode": layer.spmm.exchange,
                              "slabs": layer.spmm.slabs}
+            if name == "peer_blocks":
+                replay = layer.capture()        # the whole step as one CUDA graph
+                if replay is not None:
+                    replay()
+                    layer.spmm.x_local.mul_(2.0)    # new features in place: the graph reads the same buffers
+                    doubled = replay().clone()
+                    layer.spmm.x_local.mul_(0.5)
+                    results["graph_replay"] = {"agg": agg.cpu(), "out": replay().cpu(), "doubled": doubled.cpu(),
+                                               "mode": "graph", "slabs": 0}
             dist.barrier()
         torch.save({"results": results, "begin": int(bounds[rank]), "end": int(bounds[rank + 1])},
                    os.path.join(out_dir, f"rank{rank}.pt"))
@@ -84,4 +93,8 @@ def test_sharded_layer_on_gpus(tmp_path):
         out = torch.cat([p["results"][name]["out"] for p in parts]).double().numpy()
         scale = np.abs(expected_out).max()
         assert np.abs(out - expected_out).max() <= 2e-5 * scale, name
+    if "graph_replay" in parts[0]["results"]:
+        bias = linear.bias.detach().double().numpy()
+        doubled = torch.cat([p["results"]["graph_replay"]["doubled"] for p in parts]).double().numpy()
+        assert np.abs(doubled - (2.0 * (expected_out - bias) + bias)).max() <= 4e-5 * scale
     assert parts[0]["results"]["peer_slabs2"]["slabs"] in (0, 2)   # 0 only if symmetric memory was unavailable

@@ -296,3 +296,18 @@ def test_operators_replay_inside_a_cuda_graph(asg, orc):
     exact_s = orc.sddmm(to_np(crow), to_np(col), q_d.cpu().numpy(), k_d.cpu().numpy())
     ok, ratio = orc.within_tolerance(s.cpu().numpy(), exact_s, to_np(crow), per_edge=True)
     assert ok, ratio
+
+
+def test_debug_index_check(monkeypatch):
+    """AUTOSAGE_CHECK_INDICES=1 turns an out-of-range column into an error instead of a stray read."""
+    import autosage_b200 as asg
+
+    dev = torch.device("cuda")
+    crow = torch.tensor([0, 2, 3], device=dev)
+    col = torch.tensor([0, 1, 5], device=dev)      # 5 is outside a 2-row X
+    x = torch.ones(2, 4, device=dev)
+    monkeypatch.setenv("AUTOSAGE_CHECK_INDICES", "1")
+    with pytest.raises(RuntimeError, match="col entries must lie in"):
+        asg.spmm_csr(crow, col, None, x)
+    good = torch.tensor([0, 1, 1], device=dev)
+    assert torch.equal(asg.spmm_csr(crow, good, None, x), torch.tensor([[2.0] * 4, [1.0] * 4], device=dev))
