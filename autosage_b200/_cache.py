@@ -102,12 +102,34 @@ def graph_signature(
     }
 
 
+# Parsed schedules.json per path, valid while the file's (mtime, size, inode) is unchanged: a replayed
+# call then costs one stat() instead of reading and parsing the whole file.
+_PARSED: dict[str, tuple[tuple[int, int, int], dict[str, dict[str, Any]]]] = {}
+
+
+def _file_stamp(path: Path) -> Optional[tuple[int, int, int]]:
+    try:
+        st = os.stat(path)
+    except OSError:
+        return None
+    return (st.st_mtime_ns, st.st_size, st.st_ino)
+
+
 class ScheduleCache:
     """JSON file of schedules; every ``store`` rewrites the file through a temporary + rename."""
 
     def __init__(self, path: Optional[os.PathLike[str] | str] = None):
         self.path = Path(path) if path is not None else cache_directory() / "schedules.json"
-        self._records: dict[str, dict[str, Any]] = self._read()
+        stamp = _file_stamp(self.path)
+        memo = _PARSED.get(str(self.path))
+        if stamp is not None and memo is not None and memo[0] == stamp:
+            self._records = memo[1]
+        else:
+            self._records = self._read()
+            if stamp is not None and stamp == _file_stamp(self.path):
+                _PARSED[str(self.path)] = (stamp, self._records)
+            else:
+                _PARSED.pop(str(self.path), None)
 
     @staticmethod
     def _key(device: dict[str, Any], graph: dict[str, Any]) -> str:
@@ -142,6 +164,9 @@ class ScheduleCache:
                           indent=2, sort_keys=True)
                 out.write("\n")
             os.replace(scratch, self.path)
+            stamp = _file_stamp(self.path)
+            if stamp is not None:
+                _PARSED[str(self.path)] = (stamp, self._records)
         finally:
             if os.path.exists(scratch):
                 os.unlink(scratch)

@@ -48,6 +48,8 @@ SIGNATURES = {
     "asg_csr_row_softmax": (_INT, [_P, _P, _P, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_csr_attention": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _F32, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_add_row_bias": (_INT, [_P, _P, _I64, _I64, _P]),
+    "asg_csr_build_workspace_bytes": (_SZ, [_I64, _I64]),
+    "asg_csr_from_edges": (_INT, [_P, _P, _P, _I64, _I64, _P, _P, _P, _P, _P, _SZ, _P]),
     "asg_linear_bias": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "asg_copy_2d": (_INT, [_P, _SZ, _P, _SZ, _SZ, _SZ, _P]),
     "asg_workspace_status": (_INT, [_P, _P, _P]),
@@ -261,6 +263,28 @@ def attention(crow, col, query, key, value, out, *, scale: float, warps: int, th
 def add_row_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
     """out[r, :] += bias, in place (contiguous float32 CUDA tensors)."""
     check(library().asg_add_row_bias(out.data_ptr(), bias.data_ptr(), out.size(0), out.size(1), _stream(out.device)))
+
+
+def csr_from_edges(row_of_edge: torch.Tensor, col_of_edge: torch.Tensor, values: Optional[torch.Tensor],
+                   n_rows: int, want_order: bool):
+    """Stable COO -> CSR on the device (contiguous int64 CUDA ids, float32 values or None).
+    Returns (crow, col, order or None, permuted values or None)."""
+    device = row_of_edge.device
+    n_edges = row_of_edge.numel()
+    crow = torch.empty(n_rows + 1, dtype=torch.long, device=device)
+    col = torch.empty(n_edges, dtype=torch.long, device=device)
+    order = torch.empty(n_edges, dtype=torch.long, device=device) if want_order else None
+    permuted = torch.empty(n_edges, dtype=torch.float32, device=device) if values is not None else None
+    need = int(library().asg_csr_build_workspace_bytes(n_edges, n_rows))
+    if need == 0:
+        raise RuntimeError("asg_csr_build_workspace_bytes could not size the sort scratch")
+    workspace = torch.empty(need, dtype=torch.uint8, device=device)
+    check(library().asg_csr_from_edges(row_of_edge.data_ptr(), col_of_edge.data_ptr(),
+                                       None if values is None else values.data_ptr(), n_edges, n_rows,
+                                       crow.data_ptr(), col.data_ptr(), None if order is None else order.data_ptr(),
+                                       None if permuted is None else permuted.data_ptr(), workspace.data_ptr(),
+                                       workspace.numel(), _stream(device)))
+    return crow, col, order, permuted
 
 
 def linear_bias(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:

@@ -16,7 +16,7 @@ from torch import nn
 
 from ._auto import spmm_csr_auto
 from .ops import spmm_csr
-from .utils.csr import edge_index_to_csr
+from .utils.csr import csr_with_order, edge_index_to_csr  # noqa: F401  (edge_index_to_csr: re-exported as in the reference)
 
 
 def _tensor_core_linear_ok(linear: nn.Linear, aggregated: torch.Tensor) -> bool:
@@ -78,11 +78,11 @@ class _CsrMemo:
         same = (self._ref is not None and self._ref() is edge_index and self._version == edge_index._version
                 and self._nodes == num_nodes)
         if not same:
-            crow, col = edge_index_to_csr(edge_index, num_nodes, rows_by="dst")
+            crow, col, order, _ = csr_with_order(edge_index, num_nodes, rows_by="dst", want_order=need_order)
             self._ref, self._version, self._nodes = weakref.ref(edge_index), edge_index._version, num_nodes
-            self._value = [crow, col, None]
+            self._value = [crow, col, order]
         if need_order and self._value[2] is None:
-            self._value[2] = edge_index[1].to(torch.long).argsort(stable=True)
+            self._value[2] = csr_with_order(edge_index, num_nodes, rows_by="dst", want_order=True)[2]
         return self._value
 
 

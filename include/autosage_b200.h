@@ -161,6 +161,22 @@ int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, c
 int asg_add_row_bias(float* out, const float* bias, int64_t rows, int64_t cols, void* stream);
 
 /*
+ * COO -> CSR on the device, rows keyed by row_of_edge, edges of one row in their input order:
+ *   crow[r]  = number of edges with row id below r              (r = 0 .. n_rows; int64[n_rows + 1])
+ *   perm     = the stable ordering of the edges by row id        (int64[n_edges]; may be null)
+ *   col[i]   = col_of_edge[perm[i]]                              (int64[n_edges])
+ *   val_out[i] = val_in[perm[i]]                                 (float32[n_edges]; both may be null)
+ * Replaces edge_index_to_csr (autosage/utils/csr.py:6-26: stable argsort + bincount + cumsum + gather)
+ * and the second argsort by which AutoSAGEConv.forward permutes edge weights (autosage/conv.py:44-45).
+ * Row ids must lie in [0, n_rows); n_edges and n_rows below 2^31.  The workspace holds
+ * asg_csr_build_workspace_bytes(n_edges, n_rows) bytes (about 16 bytes per edge), 256-byte aligned.
+ */
+size_t asg_csr_build_workspace_bytes(int64_t n_edges, int64_t n_rows);
+int asg_csr_from_edges(const int64_t* row_of_edge, const int64_t* col_of_edge, const float* val_in,
+                       int64_t n_edges, int64_t n_rows, int64_t* crow, int64_t* col, int64_t* perm,
+                       float* val_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * out[rows, out_features] = x[rows, in_features] @ weight[out_features, in_features]^T + bias:
  * the layer's nn.Linear (autosage/conv.py:55) at float32 accuracy on the tensor cores (each float32
  * operand is split into three bfloat16 pieces, the piece products are summed in float32; no TF32

@@ -510,3 +510,49 @@ def test_layer_linear_uses_tensor_core_path(lib, monkeypatch):
     y = conv.apply_linear(linear, x.requires_grad_())          # gradient wanted: differentiable route
     y.sum().backward()
     assert x.grad is not None and linear.weight.grad is not None
+
+
+@pytest.mark.parametrize("nodes,edges,rows_by,dtype", [(1, 5, "dst", torch.long), (7, 0, "dst", torch.long),
+                                                       (100, 1000, "dst", torch.int32), (257, 5000, "src", torch.long),
+                                                       (5000, 200_000, "dst", torch.long),
+                                                       (300_000, 1_500_000, "dst", torch.long)])
+def test_device_csr_build_is_bit_exact(lib, monkeypatch, nodes, edges, rows_by, dtype):
+    """The device COO -> CSR build returns the integers of the torch formulation (stable within a row),
+    the edge ordering, and the permuted weights."""
+    from autosage_b200.utils import csr as csr_utils
+
+    gen = torch.Generator().manual_seed(nodes + edges)
+    edge_index = torch.randint(0, nodes, (2, edges), generator=gen).to(dtype)
+    if edges > 10:
+        edge_index[1, : edges // 3] = edge_index[1, 0]      # a hub destination and many duplicates
+    weight = torch.rand(edges, generator=gen)
+    monkeypatch.setenv("AUTOSAGE_CSR_BUILD", "torch")
+    want = csr_utils.csr_with_order(edge_index, nodes, rows_by=rows_by, want_order=True, edge_weight=weight)
+    monkeypatch.setenv("AUTOSAGE_CSR_BUILD", "native")
+    got = csr_utils.csr_with_order(edge_index.cuda(), nodes, rows_by=rows_by, want_order=True, edge_weight=weight.cuda())
+    for a, b in zip(got, want):
+        assert a.dtype == b.dtype and torch.equal(a.cpu(), b)
+    crow, col = csr_utils.edge_index_to_csr(edge_index.cuda(), nodes, rows_by=rows_by)
+    assert torch.equal(crow.cpu(), want[0]) and torch.equal(col.cpu(), want[1])
+
+
+def test_layer_forward_with_device_csr_build(lib):
+    """AutoSAGEConv from an edge list (weighted and unweighted) against the dense formulation."""
+    from autosage_b200 import AutoSAGEConv
+
+    dev = torch.device("cuda")
+    gen = torch.Generator().manual_seed(11)
+    n, e = 2000, 30000
+    edge_index = torch.randint(0, n, (2, e), generator=gen)
+    weight = torch.rand(e, generator=gen)
+    x = torch.randn(n, 64, generator=gen)
+    torch.manual_seed(0)
+    layer = AutoSAGEConv(64, 32, mode="native").to(dev)
+    dense_a = torch.zeros(n, n, dtype=torch.float64)
+    dense_a.index_put_((edge_index[1], edge_index[0]), weight.double(), accumulate=True)
+    expected = (dense_a @ x.double()) @ layer.linear.weight.detach().cpu().double().t() + layer.linear.bias.detach().cpu().double()
+    with torch.no_grad():
+        out = layer(x.to(dev), edge_index.to(dev), weight.to(dev))
+        again = layer(x.to(dev), edge_index.to(dev), weight.to(dev))
+    assert torch.allclose(out.cpu().double(), expected, rtol=1e-4, atol=1e-3)
+    assert torch.equal(out, again)

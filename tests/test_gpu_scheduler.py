@@ -99,9 +99,9 @@ def test_spmm_auto_probe_then_cache_replay(asg, orc, graph, isolated_cache):
     out, info = asg.spmm_csr_auto(crow, col, val, x)
     assert set(info) == SPMM_KEYS
     assert info["operation"] == "spmm" and info["schema_version"] == 3 and info["from_cache"] is False
-    assert info["probe_rows"] == 600 and info["guardrail"] == 0.95  # max(int(20000 * 0.03), 512)
+    assert info["probe_rows"] == 20000 and info["guardrail"] == 0.95  # a graph this small is probed whole
     assert info["baseline"] == "torch.sparse.mm(csr)"
-    assert 1 <= len(info["candidates"]) <= 6
+    assert 1 <= len(info["candidates"]) <= 7     # the shortlist of 6 plus the library default
     for entry in info["candidates"]:
         tile, warps, threshold = entry["candidate"]
         assert tile in (64, 128) and warps in (2, 4, 8) and threshold >= 1
@@ -311,3 +311,29 @@ def test_debug_index_check(monkeypatch):
         asg.spmm_csr(crow, col, None, x)
     good = torch.tensor([0, 1, 1], device=dev)
     assert torch.equal(asg.spmm_csr(crow, good, None, x), torch.tensor([[2.0] * 4, [1.0] * 4], device=dev))
+
+
+def test_probe_on_row_sample_prefers_the_kernels(asg, isolated_cache, monkeypatch):
+    """On a power-law graph the whole-row probe sample ranks the kernels ahead of the gather-dot
+    baseline (SDDMM) and records a full-graph candidate; the induced sample stays selectable."""
+    from autosage_b200 import synthetic as syn
+
+    dev = torch.device("cuda")
+    crow, col, info = syn.powerlaw_csr(syn.ARXIV_LIKE, seed=0, device=dev)
+    n = info["rows"]
+    q, k = syn.dense(n, 64, 1, dev), syn.dense(n, 64, 2, dev)
+    out, sched = asg.sddmm_csr_auto(crow, col, q, k)
+    assert sched["choice"] == "autosage" and sched["candidate"] is not None
+    assert sched["probe_rows"] == n and sched["probe_nonzeros"] == info["nnz"]   # 2.5 M edges: probed whole
+    monkeypatch.setenv("AUTOSAGE_PROBE_EDGES", "500000")                         # force a row sample
+    monkeypatch.setenv("AUTOSAGE_CACHE", "0")
+    _, sampled = asg.sddmm_csr_auto(crow, col, q, k)
+    assert sampled["choice"] == "autosage"
+    assert 0.1 * info["nnz"] < sampled["probe_nonzeros"] < 0.4 * info["nnz"] and sampled["probe_rows"] < n
+    rows = torch.repeat_interleave(torch.arange(n, device=dev), crow[1:] - crow[:-1])
+    expected = (q[rows[:100000]] * k[col[:100000]]).sum(1)
+    assert torch.allclose(out[:100000], expected, rtol=1e-4, atol=1e-4)
+    monkeypatch.setenv("AUTOSAGE_PROBE_SAMPLE", "induced")
+    monkeypatch.setenv("AUTOSAGE_CACHE", "0")
+    _, sched = asg.sddmm_csr_auto(crow, col, q, k)
+    assert sched["probe_nonzeros"] < 0.01 * info["nnz"]

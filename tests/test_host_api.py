@@ -346,3 +346,24 @@ def test_linear_helper_matches_the_module_on_cpu():
     layer = torch.nn.Linear(5, 3)
     x = torch.randn(7, 5)
     assert torch.equal(apply_linear(layer, x), layer(x))
+
+
+def test_row_sample_keeps_whole_rows():
+    """The probe's row sample: same selected rows as the induced sample, every edge of each kept."""
+    from autosage_b200 import _auto
+
+    gen = torch.Generator().manual_seed(5)
+    degree = torch.randint(0, 9, (200,), generator=gen)
+    crow = torch.cat((torch.zeros(1, dtype=torch.long), degree.cumsum(0)))
+    col = torch.randint(0, 200, (int(crow[-1]),), generator=gen)
+    val = torch.rand(col.numel(), generator=gen)
+    s_crow, s_col, s_val, rows = _auto._row_sample_csr(crow, col, val, fraction=0.25, minimum_rows=4, seed=3)
+    induced_rows = _auto._induced_sample_csr(crow, col, val, fraction=0.25, minimum_rows=4, seed=3)[3]
+    assert torch.equal(rows, induced_rows) and rows.numel() == 50
+    assert torch.equal(s_crow[1:] - s_crow[:-1], degree[rows])
+    expected_col = torch.cat([col[crow[r]:crow[r + 1]] for r in rows.tolist()])
+    expected_val = torch.cat([val[crow[r]:crow[r + 1]] for r in rows.tolist()])
+    assert torch.equal(s_col, expected_col) and torch.equal(s_val, expected_val)
+    empty = _auto._row_sample_csr(torch.zeros(11, dtype=torch.long), torch.zeros(0, dtype=torch.long), None,
+                                  fraction=0.5, minimum_rows=2, seed=0)
+    assert empty[0].tolist() == [0] * 6 and empty[1].numel() == 0 and empty[2] is None
