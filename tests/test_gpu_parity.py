@@ -534,6 +534,11 @@ def test_device_csr_build_is_bit_exact(lib, monkeypatch, nodes, edges, rows_by, 
         assert a.dtype == b.dtype and torch.equal(a.cpu(), b)
     crow, col = csr_utils.edge_index_to_csr(edge_index.cuda(), nodes, rows_by=rows_by)
     assert torch.equal(crow.cpu(), want[0]) and torch.equal(col.cpu(), want[1])
+    from oracle import oracle as orc
+
+    o_crow, o_col, o_perm = orc.edge_index_to_csr(edge_index.long().numpy(), nodes, rows_by)
+    assert np.array_equal(got[2].cpu().numpy(), o_perm)
+    assert np.array_equal(crow.cpu().numpy(), o_crow) and np.array_equal(col.cpu().numpy(), o_col)
 
 
 def test_layer_forward_with_device_csr_build(lib):
