@@ -481,8 +481,8 @@ class ShardedAutoSAGEConv(torch.nn.Module):
         is 2-3 ms of GPU work and the eager launch sequence does not always stay ahead of it.  All
         ranks must call this together; if any rank fails to capture, all return None (run eagerly)."""
         spmm = self.spmm
-        if spmm.device.type != "cuda":
-            return None
+        if spmm.device.type != "cuda" or (spmm.shard.world > 1 and spmm.exchange != "peer"):
+            return None  # the send/recv exchange is driven from the host (work.wait()), step by step
         ok = 1
         graph, out = None, None
         try:
