@@ -1,4 +1,4 @@
-"""Row-partitioned SpMM / AutoSAGEConv over the GPUs of one node (one process per GPU).
+"""Row-partitioned SpMM / SDDMM / attention / AutoSAGEConv over the GPUs of one node (one process per GPU).
 
 The reference is single-GPU.  For graphs that should be spread over 2/4/8 B200s the destination
 rows are cut into contiguous ranges balanced by nnz; rank r owns rows [b_r, b_{r+1}), the matching
@@ -459,6 +459,114 @@ class ShardedSpmm:
             for work in works:
                 work.wait()
         return y
+
+
+class _GatheredOperand:
+    """A dense operand indexed by COLUMN (K or V), gathered like X: the exchange half of a
+    ``ShardedSpmm`` without its products."""
+
+    def __init__(self, shard: RowShard, features: int, group, exchange: Optional[str]) -> None:
+        self._engine = ShardedSpmm(shard, features, group=group, exchange=exchange)
+
+    @property
+    def local(self) -> torch.Tensor:
+        return self._engine.x_local
+
+    @property
+    def full(self) -> torch.Tensor:
+        return self._engine.x_full
+
+    @property
+    def exchange(self) -> str:
+        return self._engine.exchange
+
+    def gather(self, local: Optional[torch.Tensor]) -> torch.Tensor:
+        if local is not None and local.data_ptr() != self.local.data_ptr():
+            self.local.copy_(local)
+        self._engine.exchange_only()
+        return self.full
+
+
+def _cpu_sddmm(crow, col, query, key) -> torch.Tensor:
+    rows = torch.repeat_interleave(torch.arange(crow.numel() - 1, device=crow.device), crow[1:] - crow[:-1])
+    return (query.index_select(0, rows) * key.index_select(0, col)).sum(dim=1)
+
+
+def _cpu_row_softmax(crow, scores) -> torch.Tensor:
+    if scores.numel() == 0:
+        return scores.clone()
+    rows = torch.repeat_interleave(torch.arange(crow.numel() - 1, device=crow.device), crow[1:] - crow[:-1])
+    peak = torch.full((crow.numel() - 1,), -torch.inf, dtype=scores.dtype, device=scores.device)
+    peak.scatter_reduce_(0, rows, scores, reduce="amax", include_self=True)
+    shifted = (scores - peak.index_select(0, rows)).exp()
+    total = torch.zeros_like(peak).scatter_add_(0, rows, shifted)
+    return shifted / total.index_select(0, rows)
+
+
+class ShardedSddmm:
+    """SDDMM over a row shard: ``out[e] = <Q[row(e)], K[col[e]]>`` for the shard's edges.  Q is
+    row-local; K is gathered over NVLink exactly like X (every shard's rows into a full-height
+    buffer), then the SDDMM kernels run over the local rows against the gathered K."""
+
+    def __init__(self, shard: RowShard, features: int, *, group=None, warps: int = 8, threshold: int = 8192,
+                 exchange: Optional[str] = None) -> None:
+        self.shard, self.warps, self.threshold = shard, warps, threshold
+        self.keys = _GatheredOperand(shard, features, group, exchange)
+        self._workspace = None
+        self._plan_ready = False
+
+    def forward(self, query_local: torch.Tensor, key_local: Optional[torch.Tensor] = None) -> torch.Tensor:
+        shard = self.shard
+        key_full = self.keys.gather(key_local)
+        if not query_local.is_cuda:
+            return _cpu_sddmm(shard.crow, shard.col, query_local, key_full)
+        query = query_local.contiguous()
+        out = torch.empty(shard.col.numel(), dtype=query.dtype, device=query.device)
+        if out.numel() == 0:
+            return out
+        if self._workspace is None:
+            self._workspace = torch.empty(_native.workspace_bytes(shard.n_local), dtype=torch.uint8, device=query.device)
+        _native.sddmm(shard.crow, shard.col, query, key_full, out, warps=self.warps, threshold=self.threshold,
+                      flags=_native.FLAG_PLAN_READY if self._plan_ready else 0, workspace=self._workspace)
+        self._plan_ready = True
+        return out
+
+
+class ShardedAttention:
+    """softmax_row(scale * Q K^T on the shard's CSR pattern) V for the shard's rows.  Q is row-local;
+    K and V are gathered like X; the fused one-pass kernel then runs over the local rows."""
+
+    def __init__(self, shard: RowShard, features: int, *, group=None, warps: int = 8, threshold: int = 512,
+                 exchange: Optional[str] = None) -> None:
+        if features > 512:
+            raise ValueError("the fused attention kernel takes at most 512 features")
+        self.shard, self.warps, self.threshold = shard, warps, threshold
+        self.keys = _GatheredOperand(shard, features, group, exchange)
+        self.values = _GatheredOperand(shard, features, group, exchange)
+        self._workspace = None
+        self._plan_ready = False
+
+    def forward(self, query_local: torch.Tensor, key_local: Optional[torch.Tensor] = None,
+                value_local: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+        shard = self.shard
+        key_full = self.keys.gather(key_local)
+        value_full = self.values.gather(value_local)
+        if not query_local.is_cuda:
+            scores = _cpu_sddmm(shard.crow, shard.col, query_local * scale, key_full)
+            weights = _cpu_row_softmax(shard.crow, scores)
+            matrix = torch.sparse_csr_tensor(shard.crow, shard.col, weights, size=(shard.n_local, shard.n_global))
+            return torch.sparse.mm(matrix, value_full)
+        query = query_local.contiguous()
+        out = torch.empty_like(query)
+        if out.numel() == 0:
+            return out
+        if self._workspace is None:
+            self._workspace = torch.empty(_native.workspace_bytes(shard.n_local), dtype=torch.uint8, device=query.device)
+        _native.attention(shard.crow, shard.col, query, key_full, value_full, out, scale=float(scale), warps=self.warps,
+                          threshold=self.threshold, flags=_native.FLAG_PLAN_READY if self._plan_ready else 0,
+                          workspace=self._workspace)
+        self._plan_ready = True
+        return out
 
 
 class ShardedAutoSAGEConv(torch.nn.Module):

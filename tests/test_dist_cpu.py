@@ -137,6 +137,37 @@ def test_sharded_conv_on_gloo_ranks(tmp_path, world, overlap, groups):
     assert torch.allclose(torch.cat([p["out"] for p in parts]), expected, rtol=1e-4, atol=1e-4)
 
 
+def _attention_worker(rank: int, world: int, port: int, out_dir: str):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        crow, col = random_csr(300, 7, seed=13, hubs={5: 400})
+        q, k, v = dense(300, 16, 1), dense(300, 16, 2), dense(300, 16, 3)
+        bounds = asg_dist.partition_rows(crow, world)
+        shard = asg_dist.shard_csr(crow, col, None, rank, world, bounds)
+        mine = slice(shard.row_begin, shard.row_end)
+        scores = asg_dist.ShardedSddmm(shard, 16).forward(q[mine], k[mine])
+        out = asg_dist.ShardedAttention(shard, 16).forward(q[mine], k[mine], v[mine], scale=0.25)
+        torch.save({"scores": scores, "out": out}, os.path.join(out_dir, f"rank{rank}.pt"))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_sddmm_and_attention_on_gloo_ranks(tmp_path):
+    """Q row-local, K and V gathered like X: the shards' results concatenate to the whole-graph ones."""
+    world = 2
+    mp.spawn(_attention_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    crow, col = random_csr(300, 7, seed=13, hubs={5: 400})
+    q, k, v = dense(300, 16, 1), dense(300, 16, 2), dense(300, 16, 3)
+    parts = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    exact_scores = orc.sddmm(to_np(crow), to_np(col), to_np(q), to_np(k))
+    np.testing.assert_allclose(torch.cat([p["scores"] for p in parts]).numpy(), exact_scores, rtol=1e-4, atol=1e-4)
+    exact_out = orc.attention(to_np(crow), to_np(col), to_np(q), to_np(k), to_np(v), 0.25)
+    np.testing.assert_allclose(torch.cat([p["out"] for p in parts]).numpy(), exact_out, rtol=1e-4, atol=1e-4)
+
+
 def _failing_worker(rank: int, world: int, port: int, out_dir: str):
     """Rank 1 leaves between steps (after a completed step, nothing in flight); rank 0 must get an
     error from its next exchange instead of waiting forever."""

@@ -64,6 +64,17 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
                     results["graph_replay"] = {"agg": agg.cpu(), "out": replay().cpu(), "doubled": doubled.cpu(),
                                                "mode": "graph", "slabs": 0}
             dist.barrier()
+        # SDDMM and fused attention over the shard: Q row-local, K and V gathered like X
+        shard = asg_dist.shard_csr(crow, col, None, rank, world, bounds, device=device)
+        mine = slice(shard.row_begin, shard.row_end)
+        q, k = dense(6000, 128, 6), dense(6000, 128, 7)
+        sddmm = asg_dist.ShardedSddmm(shard, 128)
+        attention = asg_dist.ShardedAttention(shard, 128)
+        for _ in range(2):
+            scores = sddmm.forward(q[mine].to(device), k[mine].to(device))
+            attended = attention.forward(q[mine].to(device), k[mine].to(device), x[mine].to(device), scale=128 ** -0.5)
+        results["sddmm"] = {"scores": scores.cpu(), "attended": attended.cpu(), "mode": sddmm.keys.exchange}
+        dist.barrier()
         torch.save({"results": results, "begin": int(bounds[rank]), "end": int(bounds[rank + 1])},
                    os.path.join(out_dir, f"rank{rank}.pt"))
         dist.barrier()
@@ -86,6 +97,15 @@ def test_sharded_layer_on_gpus(tmp_path):
     torch.manual_seed(0)
     linear = torch.nn.Linear(128, 16)       # the layers above draw their weights from the same seed
     expected_out = exact @ linear.weight.detach().double().numpy().T + linear.bias.detach().double().numpy()
+    sharded = [p["results"].pop("sddmm") for p in parts]
+    q, k = dense(6000, 128, 6), dense(6000, 128, 7)
+    ok, ratio = orc.within_tolerance(torch.cat([p["scores"] for p in sharded]).numpy(),
+                                     orc.sddmm(to_np(crow), to_np(col), to_np(q), to_np(k)), to_np(crow), per_edge=True)
+    assert ok, ("sddmm", ratio)
+    ok, ratio = orc.within_tolerance(torch.cat([p["attended"] for p in sharded]).numpy(),
+                                     orc.attention(to_np(crow), to_np(col), to_np(q), to_np(k), to_np(x), 128 ** -0.5),
+                                     to_np(crow))
+    assert ok, ("attention", ratio)
     for name in parts[0]["results"]:
         agg = torch.cat([p["results"][name]["agg"] for p in parts]).numpy()
         ok, ratio = orc.within_tolerance(agg, exact, to_np(crow))
