@@ -64,6 +64,18 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
                     results["graph_replay"] = {"agg": agg.cpu(), "out": replay().cpu(), "doubled": doubled.cpu(),
                                                "mode": "graph", "slabs": 0}
             dist.barrier()
+        # a graph whose first row holds most of the edges: some rank ends up with no rows at all
+        e_crow, e_col = random_csr(40, 2, seed=1, hubs={0: 4000})
+        e_x = dense(40, 64, 2)
+        e_bounds = asg_dist.partition_rows(e_crow, world)
+        e_shard = asg_dist.shard_csr(e_crow, e_col, None, rank, world, e_bounds, device=device)
+        torch.manual_seed(0)
+        e_layer = asg_dist.ShardedAutoSAGEConv(e_shard, 64, 8).to(device)
+        with torch.no_grad():
+            e_layer(e_x[e_shard.row_begin:e_shard.row_end].to(device))
+            e_agg = e_layer.spmm.forward()
+        results["empty_shard"] = {"agg": e_agg.cpu(), "rows": e_shard.n_local}
+        dist.barrier()
         # SDDMM and fused attention over the shard: Q row-local, K and V gathered like X
         shard = asg_dist.shard_csr(crow, col, None, rank, world, bounds, device=device)
         mine = slice(shard.row_begin, shard.row_end)
@@ -97,6 +109,12 @@ def test_sharded_layer_on_gpus(tmp_path):
     torch.manual_seed(0)
     linear = torch.nn.Linear(128, 16)       # the layers above draw their weights from the same seed
     expected_out = exact @ linear.weight.detach().double().numpy().T + linear.bias.detach().double().numpy()
+    lopsided = [p["results"].pop("empty_shard") for p in parts]
+    e_crow, e_col = random_csr(40, 2, seed=1, hubs={0: 4000})
+    assert world < 3 or min(p["rows"] for p in lopsided) == 0
+    ok, ratio = orc.within_tolerance(torch.cat([p["agg"] for p in lopsided]).numpy(),
+                                     orc.spmm(to_np(e_crow), to_np(e_col), None, to_np(dense(40, 64, 2))), to_np(e_crow))
+    assert ok, ("empty shard", ratio)
     sharded = [p["results"].pop("sddmm") for p in parts]
     q, k = dense(6000, 128, 6), dense(6000, 128, 7)
     ok, ratio = orc.within_tolerance(torch.cat([p["scores"] for p in sharded]).numpy(),
