@@ -2,6 +2,7 @@ from __future__ import annotations
 
 import os
 import sys
+import tempfile
 from pathlib import Path
 
 import pytest
@@ -11,7 +12,7 @@ if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
 # keep schedule caches and probe logs of the tests out of the user's home directory
-os.environ.setdefault("AUTOSAGE_CACHE_DIR", str(ROOT / "gpurun_out" / "test_cache"))
+os.environ.setdefault("AUTOSAGE_CACHE_DIR", tempfile.mkdtemp(prefix="autosage-test-cache-"))
 os.environ.setdefault("AUTOSAGE_LOG_PROBES", "0")
 
 

@@ -47,7 +47,9 @@ def random_csr(rows: int, mean_degree: int, seed: int, hub: int = 0):
 
 
 def main() -> None:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/generate.py <path of the reference checkout>")
+    root = sys.argv[1]
     ref = load_reference(root)
     from autosage_ref import _auto, _cache, config, ops  # type: ignore
     from autosage_ref.utils.csr import edge_index_to_csr  # type: ignore
