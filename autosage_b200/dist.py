@@ -92,15 +92,23 @@ def arrival_order(rank: int, world: int) -> list[int]:
     return [(rank + s) % world for s in range(world)]
 
 
-def column_groups(rank: int, world: int, groups: Optional[int] = None) -> list[list[int]]:
-    """The arrival order cut into ``groups`` runs of consecutive arrivals (all of them when None).
+def column_groups(rank: int, world: int, groups=None) -> list[list[int]]:
+    """The arrival order cut into runs of consecutive arrivals: ``groups`` equal runs when it is an
+    int (all singletons when None), or runs of the given sizes when it is a sequence summing to
+    ``world`` (e.g. (1, 3, 3, 1): the rank's own columns alone, so the first product needs no
+    transfer, and a one-owner last group, so little work is left after the last arrival).
     The SpMM of a group can start once its last member has arrived."""
     order = arrival_order(rank, world)
-    k = world if groups is None else max(1, min(int(groups), world))
-    base, extra = divmod(world, k)
+    if groups is not None and not isinstance(groups, int):
+        sizes = [int(v) for v in groups]
+        if any(v < 1 for v in sizes) or sum(sizes) != world:
+            raise ValueError(f"group sizes {sizes} must be positive and sum to the world size {world}")
+    else:
+        k = world if groups is None else max(1, min(int(groups), world))
+        base, extra = divmod(world, k)
+        sizes = [base + (1 if g < extra else 0) for g in range(k)]
     out, start = [], 0
-    for g in range(k):
-        size = base + (1 if g < extra else 0)
+    for size in sizes:
         out.append(order[start:start + size])
         start += size
     return out

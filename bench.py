@@ -511,13 +511,17 @@ def main() -> None:
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-other-configs", action="store_true",
                         help="N = 1: skip the short runs of configurations 2, 3 and 4")
-    parser.add_argument("--groups", type=int, default=None, help="column groups per GPU in the sharded path")
+    parser.add_argument("--groups", default=None,
+                        help="sharded path: number of column groups per GPU, or their sizes in arrival order "
+                             "(e.g. 1,3,3,1 for 8 GPUs: own columns first, one owner last)")
     parser.add_argument("--slabs", type=int, default=0, help="feature bands of the slab exchange (sharded path; 0 = column blocks)")
     parser.add_argument("--copy-streams", type=int, default=1, help="streams used for the peer pulls (sharded path)")
     parser.add_argument("--no-graph", action="store_true",
                         help="sharded path: launch every step eagerly instead of replaying a CUDA graph")
     parser.add_argument("--exchange", default=None, choices=["peer", "nccl"], help="how X is gathered (sharded path)")
     args = parser.parse_args()
+    if args.groups is not None:
+        args.groups = [int(v) for v in args.groups.split(",")] if "," in args.groups else int(args.groups)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if args.workload is None:

@@ -87,6 +87,13 @@ def test_column_groups_follow_arrival_order():
         np.testing.assert_allclose(acc, exact, rtol=1e-12, atol=1e-12)
 
 
+def test_explicit_group_sizes():
+    assert asg_dist.column_groups(2, 8, (1, 3, 3, 1)) == [[2], [3, 4, 5], [6, 7, 0], [1]]
+    assert asg_dist.column_groups(0, 4, 2) == [[0, 1], [2, 3]]
+    with pytest.raises(ValueError):
+        asg_dist.column_groups(0, 8, (4, 3))
+
+
 def _free_port() -> int:
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
