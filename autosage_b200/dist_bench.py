@@ -181,7 +181,11 @@ def run(args):
     barrier()
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with bench.ClockSampler(local_rank) as clocks:
+    sampler = bench.ClockSampler(local_rank)  # NVML set up and queried once before anything is timed
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    with sampler as clocks:
         host_begin = time.perf_counter()
         begin.record(stream)
         for _ in range(args.steps):

@@ -90,6 +90,12 @@ class ClockSampler:
             self._nvml = pynvml
             self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
             self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            # the first query of each kind is the slow one (milliseconds): make it here, outside any
+            # timed region, so that the samples taken during a run cost microseconds
+            pynvml.nvmlDeviceGetClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+            getter = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(
+                pynvml, "nvmlDeviceGetCurrentClocksThrottleReasons")
+            getter(self._handle)
         except Exception:  # NVML missing: report nulls
             self._handle = None
 
