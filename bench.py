@@ -48,6 +48,7 @@ NCU_DRAM_TRAFFIC = {
     ("c2_spmm", 128, 64): (6.04e9, "profiles/spmm_kernel_c2_f128.md"),
     ("c5_spmm", 128, 128): (60.19e9, "profiles/spmm_kernel_c5_f128.md"),
     ("c4_attention", 128, 64): (1.52e9, "profiles/attention_kernel_c4_f128.md"),
+    ("c3_sddmm", 128, 64): (5.89e9, "profiles/sddmm_kernel_c3_f128.md"),
 }
 
 
