@@ -125,7 +125,8 @@ def _stream(device: torch.device) -> int:
 # rebuild the plan, and a small LRU of buffers holding finished plans is keyed by the crow tensor.
 # --------------------------------------------------------------------------------------------
 _SCRATCH: dict[tuple[int, int], torch.Tensor] = {}
-_PLANS: "OrderedDict[tuple, tuple]" = OrderedDict()
+_PLANS: "OrderedDict[tuple, list]" = OrderedDict()   # key -> [crow weakref, crow version, buffer, plan built?]
+_UNBUILT: dict[int, list] = {}                       # buffer address -> entry whose plan no kernel has built yet
 PLAN_CACHE_ENTRIES = 16
 
 
@@ -133,8 +134,16 @@ def workspace_bytes(n_rows: int) -> int:
     return int(library().asg_workspace_bytes(int(n_rows)))
 
 
+def _capturing() -> bool:
+    return torch.cuda.is_current_stream_capturing()
+
+
 def scratch(device: torch.device, n_rows: int) -> torch.Tensor:
     need = workspace_bytes(n_rows)
+    if _capturing():
+        # a captured launch keeps the raw pointer: the buffer has to come from the graph's own pool
+        # (and so live as long as the graph), not from a cache that may replace it later
+        return torch.empty(max(need, 256), dtype=torch.uint8, device=device)
     key = (device.index if device.index is not None else torch.cuda.current_device(), _stream(device))
     buffer = _SCRATCH.get(key)
     if buffer is None or buffer.numel() < need:
@@ -147,27 +156,49 @@ def planned_workspace(crow: torch.Tensor, threshold: int) -> tuple[torch.Tensor,
     """Workspace holding the degree-binned plan of ``crow`` for ``threshold``.
 
     Returns ``(buffer, flags)`` where flags is ``FLAG_PLAN_READY`` when the buffer already holds
-    the plan (same tensor object, same version counter) and 0 when the callee must build it.
+    the plan (same tensor object, same version counter, and an earlier call that built it returned
+    without error) and 0 when the callee must build it.
+
+    While the current stream is being captured into a CUDA graph the cache is bypassed: the graph
+    records raw pointers, and a cached buffer can be evicted (or its plan replaced) long before the
+    graph is replayed.  The buffer is then allocated inside the capture, so it belongs to the graph's
+    memory pool, and the plan is rebuilt by the captured launches themselves.
     """
-    if os.getenv("AUTOSAGE_PLAN_CACHE", "1") in ("0", "false", "off", "no"):
+    if _capturing() or os.getenv("AUTOSAGE_PLAN_CACHE", "1") in ("0", "false", "off", "no"):
         return scratch(crow.device, crow.numel() - 1), 0
     key = (crow.data_ptr(), crow.numel(), int(threshold), crow.device.index, _stream(crow.device))
     entry = _PLANS.get(key)
     if entry is not None:
-        ref, version, buffer = entry
+        ref, version, buffer, built = entry
         if ref() is crow and version == crow._version:
             _PLANS.move_to_end(key)
-            return buffer, FLAG_PLAN_READY
-        del _PLANS[key]
+            return buffer, (FLAG_PLAN_READY if built else 0)
+        _forget(key)
     buffer = torch.empty(max(workspace_bytes(crow.numel() - 1), 256), dtype=torch.uint8, device=crow.device)
-    _PLANS[key] = (weakref.ref(crow), crow._version, buffer)
+    entry = [weakref.ref(crow), crow._version, buffer, False]
+    _PLANS[key] = entry
+    _UNBUILT[buffer.data_ptr()] = entry
     while len(_PLANS) > PLAN_CACHE_ENTRIES:
-        _PLANS.popitem(last=False)
+        _forget(next(iter(_PLANS)))
     return buffer, 0
+
+
+def _forget(key) -> None:
+    entry = _PLANS.pop(key, None)
+    if entry is not None:
+        _UNBUILT.pop(entry[2].data_ptr(), None)
+
+
+def _plan_was_built(workspace: torch.Tensor) -> None:
+    """Called after a launch that (re)builds the plan returned without error."""
+    entry = _UNBUILT.pop(workspace.data_ptr(), None) if _UNBUILT else None
+    if entry is not None:
+        entry[3] = True
 
 
 def clear_plan_cache() -> None:
     _PLANS.clear()
+    _UNBUILT.clear()
     _SCRATCH.clear()
 
 
@@ -177,6 +208,7 @@ def clear_plan_cache() -> None:
 def plan_build(crow: torch.Tensor, threshold: int, workspace: torch.Tensor) -> None:
     check(library().asg_plan_build(crow.data_ptr(), crow.numel() - 1, int(threshold), workspace.data_ptr(),
                                    workspace.numel(), _stream(crow.device)))
+    _plan_was_built(workspace)
 
 
 def plan_export(workspace: torch.Tensor, n_rows: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -193,6 +225,7 @@ def spmm(crow, col, val, x, y, *, feature_tile: int, warps: int, threshold: int,
                                     y.size(0), col.numel(), x.size(1), int(feature_tile), int(warps),
                                     int(threshold), int(flags), workspace.data_ptr(), workspace.numel(),
                                     _stream(x.device)))
+    _plan_was_built(workspace)
 
 
 def spmm_range(crow, col, val, x, y, *, feature_begin: int, feature_count: int, feature_tile: int, warps: int,
@@ -202,6 +235,7 @@ def spmm_range(crow, col, val, x, y, *, feature_begin: int, feature_count: int, 
                                        y.size(0), col.numel(), x.size(1), int(feature_begin), int(feature_count),
                                        int(feature_tile), int(warps), int(threshold), int(flags),
                                        workspace.data_ptr(), workspace.numel(), _stream(x.device)))
+    _plan_was_built(workspace)
 
 
 def copy_columns(dst: torch.Tensor, src: torch.Tensor, column_begin: int, column_count: int) -> None:
@@ -218,12 +252,14 @@ def spmm_split_strict(crow, col, val, x, y, feature_tile: int, warps: int, thres
     check(library().asg_spmm_csr_split(crow.data_ptr(), col.data_ptr(), _ptr(val), x.data_ptr(), y.data_ptr(),
                                        y.size(0), col.numel(), x.size(1), int(feature_tile), int(warps),
                                        int(threshold), workspace.data_ptr(), workspace.numel(), _stream(x.device)))
+    _plan_was_built(workspace)
 
 
 def spmm_plain(crow, col, val, x, y, workspace: torch.Tensor) -> None:
     check(library().asg_spmm_csr(crow.data_ptr(), col.data_ptr(), _ptr(val), x.data_ptr(), y.data_ptr(),
                                  y.size(0), col.numel(), x.size(1), workspace.data_ptr(), workspace.numel(),
                                  _stream(x.device)))
+    _plan_was_built(workspace)
 
 
 def sddmm(crow, col, query, key, out, *, warps: int, threshold: int, flags: int, workspace: torch.Tensor) -> None:
@@ -231,6 +267,7 @@ def sddmm(crow, col, query, key, out, *, warps: int, threshold: int, flags: int,
                                      out.data_ptr(), query.size(0), col.numel(), query.size(1), int(warps),
                                      int(threshold), int(flags), workspace.data_ptr(), workspace.numel(),
                                      _stream(query.device)))
+    _plan_was_built(workspace)
 
 
 def sddmm_split_strict(crow, col, query, key, out, warps: int, threshold: int, workspace: torch.Tensor) -> None:
@@ -238,18 +275,21 @@ def sddmm_split_strict(crow, col, query, key, out, warps: int, threshold: int, w
                                         out.data_ptr(), query.size(0), col.numel(), query.size(1), int(warps),
                                         int(threshold), workspace.data_ptr(), workspace.numel(),
                                         _stream(query.device)))
+    _plan_was_built(workspace)
 
 
 def sddmm_plain(crow, col, query, key, out, workspace: torch.Tensor) -> None:
     check(library().asg_sddmm_csr(crow.data_ptr(), col.data_ptr(), query.data_ptr(), key.data_ptr(),
                                   out.data_ptr(), query.size(0), col.numel(), query.size(1),
                                   workspace.data_ptr(), workspace.numel(), _stream(query.device)))
+    _plan_was_built(workspace)
 
 
 def row_softmax(crow, scores, probs, *, warps: int, threshold: int, flags: int, workspace: torch.Tensor) -> None:
     check(library().asg_csr_row_softmax(crow.data_ptr(), scores.data_ptr(), probs.data_ptr(), crow.numel() - 1,
                                         scores.numel(), int(warps), int(threshold), int(flags),
                                         workspace.data_ptr(), workspace.numel(), _stream(scores.device)))
+    _plan_was_built(workspace)
 
 
 def attention(crow, col, query, key, value, out, *, scale: float, warps: int, threshold: int, flags: int,
@@ -258,6 +298,7 @@ def attention(crow, col, query, key, value, out, *, scale: float, warps: int, th
                                       value.data_ptr(), out.data_ptr(), query.size(0), col.numel(),
                                       query.size(1), float(scale), int(warps), int(threshold), int(flags),
                                       workspace.data_ptr(), workspace.numel(), _stream(query.device)))
+    _plan_was_built(workspace)
 
 
 def add_row_bias(out: torch.Tensor, bias: torch.Tensor) -> None:

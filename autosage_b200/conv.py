@@ -25,7 +25,9 @@ def _tensor_core_linear_ok(linear: nn.Linear, aggregated: torch.Tensor) -> bool:
     if torch.is_grad_enabled() and (aggregated.requires_grad or any(p.requires_grad for p in linear.parameters())):
         return False
     weight, bias = linear.weight, linear.bias
-    return (weight.dtype == torch.float32 and weight.is_cuda and weight.device == aggregated.device
+    # the kernel moves 16-byte vectors: a parameter that is a view into a flat buffer may start elsewhere
+    aligned = all(t is None or t.data_ptr() % 16 == 0 for t in (aggregated, weight, bias))
+    return (aligned and weight.dtype == torch.float32 and weight.is_cuda and weight.device == aggregated.device
             and (bias is None or bias.dtype == torch.float32)
             and aggregated.size(1) % 4 == 0 and weight.size(0) % 4 == 0 and aggregated.size(0) < 2 ** 31)
 
@@ -84,6 +86,10 @@ class _CsrMemo:
         if need_order and self._value[2] is None:
             self._value[2] = csr_with_order(edge_index, num_nodes, rows_by="dst", want_order=True)[2]
         return self._value
+
+    def __reduce__(self):
+        # the memo is a cache keyed by a weak reference: a pickled / saved / spawned layer starts without it
+        return (_CsrMemo, ())
 
 
 class AutoSAGEConv(nn.Module):

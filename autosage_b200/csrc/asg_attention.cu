@@ -218,13 +218,8 @@ __device__ __forceinline__ void attention_batches(const AttentionArgs& a, int ro
   }
 }
 
-#ifdef ASG_ATTN_MIN_BLOCKS  // e.g. 2 caps the kernel at 64 registers per thread
-#define ASG_BOUNDS __launch_bounds__(512, ASG_ATTN_MIN_BLOCKS)
-#else
-#define ASG_BOUNDS __launch_bounds__(512)
-#endif
 template <int VW, int G, int NV, int U>
-__global__ void ASG_BOUNDS attention_kernel(const AttentionArgs a) {
+__global__ void __launch_bounds__(512) attention_kernel(const AttentionArgs a) {
   pdl_release_dependents();  // the short-row kernel may move in as CTAs of this one retire
   constexpr int FT = VW * G * NV;
   extern __shared__ __align__(16) unsigned char smem[];
@@ -439,12 +434,10 @@ static int launch_attention_instance(const AttentionArgs& args, int warps, cudaS
 
 static bool aligned_to(const void* p, size_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; }
 
-#ifndef ASG_ATTN_U
-#define ASG_ATTN_U 8
-#endif
+constexpr int kAttentionLoadsInFlight = 8;  // gather instructions issued per lane before their results are used
 
 static int launch_attention(const AttentionArgs& args, int vw, int warps, cudaStream_t stream, int device) {
-  constexpr int U = ASG_ATTN_U;
+  constexpr int U = kAttentionLoadsInFlight;
   const int f = args.f;
   if (vw == 8) {
     if (f <= 32) return launch_attention_instance<8, 4, 1, U / 2>(args, warps, stream, device);
@@ -536,9 +529,6 @@ int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, c
     if (f % 8 == 0 && a32) vw = 8;
     else if (f % 4 == 0 && a16) vw = 4;
   }
-#ifdef ASG_ATTN_MAX_VW
-  if (vw > ASG_ATTN_MAX_VW) vw = ASG_ATTN_MAX_VW;
-#endif
   AttentionArgs args;
   args.crow = crow;
   args.col = col;

@@ -8,7 +8,10 @@
 // instead of eight; CUB's DeviceRadixSort, which is stable), and one gather pass writes the column
 // array, the permutation and the permuted weights together.  Row pointers come from a binary search of
 // the sorted keys (no atomics, no scan): crow[r] = number of edges whose row id is below r, which is
-// also what bincount + cumsum give, including for ids at or beyond n_rows.
+// what bincount + cumsum give.  Row ids must lie in [0, n_rows): only the low key_bits(n_rows) bits of
+// an id take part in the sort, so an id outside that range would be placed by its low bits and the row
+// pointers would no longer describe the column array.  The kernels do not check this (the Python
+// caller does under AUTOSAGE_CHECK_INDICES=1).
 #include "asg_common.cuh"
 
 #include <cub/device/device_radix_sort.cuh>

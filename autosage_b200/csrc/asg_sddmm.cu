@@ -85,13 +85,8 @@ __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, l
   }
 }
 
-#ifdef ASG_SDDMM_MIN_BLOCKS  // e.g. 2 caps the kernel at 64 registers per thread
-#define ASG_BOUNDS __launch_bounds__(512, ASG_SDDMM_MIN_BLOCKS)
-#else
-#define ASG_BOUNDS __launch_bounds__(512)
-#endif
 template <int VW, int G, int NV, int U>
-__global__ void ASG_BOUNDS sddmm_kernel(const SddmmArgs a) {
+__global__ void __launch_bounds__(512) sddmm_kernel(const SddmmArgs a) {
   pdl_release_dependents();  // the short-row kernel may move in as CTAs of this one retire
   __shared__ int s_item;
   const int tid = threadIdx.x;
@@ -239,9 +234,7 @@ static int launch_instance(const SddmmArgs& args, int warps, cudaStream_t stream
   return ASG_OK;
 }
 
-#ifndef ASG_SDDMM_U
-#define ASG_SDDMM_U 8
-#endif
+constexpr int kSddmmLoadsInFlight = 8;  // gather instructions issued per lane before their results are used
 
 // K larger than this (bytes) no longer sits comfortably in L2 next to the streamed CSR and output:
 // the product is then computed in passes of 64 features.
@@ -250,7 +243,7 @@ constexpr long long kTilePassBytes = 64ll << 20;
 // Picks the narrowest tile that covers f (so Q stays in registers); above 512 floats the tile is
 // 512 wide and Q is re-read per batch.
 static int launch_sddmm(SddmmArgs& args, int vw, cudaStream_t stream, int warps, int device) {
-  constexpr int U = ASG_SDDMM_U;
+  constexpr int U = kSddmmLoadsInFlight;
   const int f = args.f;
   auto tiles = [&](int ft) { args.n_tiles = (f + ft - 1) / ft; };
   if (vw == 8 && args.fixed_tile == kTilePasses) {
@@ -311,9 +304,6 @@ static int sddmm_entry(const int64_t* crow, const int64_t* col, const float* q, 
     if (f % 8 == 0 && aligned_to(q, 32) && aligned_to(k, 32)) vw = 8;
     else if (f % 4 == 0 && aligned_to(q, 16) && aligned_to(k, 16)) vw = 4;
   }
-#ifdef ASG_SDDMM_MAX_VW
-  if (vw > ASG_SDDMM_MAX_VW) vw = ASG_SDDMM_MAX_VW;
-#endif
   SddmmArgs args;
   args.crow = crow;
   args.col = col;

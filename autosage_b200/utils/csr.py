@@ -17,9 +17,21 @@ def _torch_build(row_of_edge, col_of_edge, num_nodes: int, device):
     permutation = torch.argsort(row_of_edge, stable=True)
     counts = torch.bincount(row_of_edge, minlength=num_nodes) if row_of_edge.numel() else torch.zeros(
         num_nodes, dtype=torch.long, device=device)
+    if counts.numel() > num_nodes:  # the reference's index_add_ raises here as well
+        raise IndexError(f"edge_index holds a row id outside [0, {num_nodes})")
     crow = torch.zeros(num_nodes + 1, dtype=torch.long, device=device)
-    torch.cumsum(counts[:num_nodes], 0, out=crow[1:])
+    torch.cumsum(counts, 0, out=crow[1:])
     return crow.contiguous(), col_of_edge[permutation].contiguous(), permutation
+
+
+def _debug_check_row_ids(row_of_edge: torch.Tensor, num_nodes: int) -> None:
+    """AUTOSAGE_CHECK_INDICES=1: the device build sorts only the bits a valid row id can have, so an id
+    outside [0, num_nodes) would silently corrupt the CSR; check the range first (synchronises)."""
+    if os.getenv("AUTOSAGE_CHECK_INDICES") != "1" or row_of_edge.numel() == 0:
+        return
+    low, high = int(row_of_edge.min().item()), int(row_of_edge.max().item())
+    if low < 0 or high >= num_nodes:
+        raise IndexError(f"edge_index holds a row id outside [0, {num_nodes}): found [{low}, {high}]")
 
 
 def _native_build_ok(row_of_edge: torch.Tensor, num_nodes: int) -> bool:
@@ -44,6 +56,8 @@ def csr_with_order(edge_index: torch.Tensor, num_nodes: int, *, rows_by: str = "
     row_of_edge, col_of_edge = (dst, src) if rows_by == "dst" else (src, dst)
     if _native_build_ok(row_of_edge, num_nodes):
         from .. import _native
+
+        _debug_check_row_ids(row_of_edge, num_nodes)
 
         values = None
         if edge_weight is not None and edge_weight.dtype == torch.float32 and not (

@@ -6,7 +6,7 @@
 One "step" is one pass of the hot path (one SpMM / SDDMM / attention call) over the whole synthetic
 graph.  Metric: algorithmic GB/s (bytes = CSR + gathered dense rows + output, the byte model of the
 roofline) with edges*F/s alongside.  The default workload at every N is the AutoSAGEConv forward of
-BASELINE configuration 5 (2,449,029 rows, ~123.7 M nnz, F = 128, Linear F->256), the configuration the
+the ogbn-products-sized power-law graph (2,449,029 rows, ~123.7 M nnz, F = 128, Linear F->256), the configuration the
 1/2/4/8-GPU series is quoted on: at N = 1 the whole graph on one GPU, at N > 1 rows sharded by nnz over
 the ranks with X gathered over NVLink inside the timed region (peer-memory pulls, or NCCL send/recv
 with --exchange nccl); strong scaling, and each multi-GPU line also carries the same layer timed on
@@ -41,15 +41,16 @@ import torch  # noqa: E402
 
 FALLBACK_HBM_GBS = 6650.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (key: workload, F, feature tile).  Workloads without a capture
-# of the byte counters report null.
-NCU_DRAM_TRAFFIC = {
-    ("c2_spmm", 128, 64): (6.04e9, "profiles/spmm_kernel_c2_f128.md"),
-    ("c5_spmm", 128, 128): (60.19e9, "profiles/spmm_kernel_c5_f128.md"),
-    ("c4_attention", 128, 64): (1.52e9, "profiles/attention_kernel_c4_f128.md"),
-    ("c3_sddmm", 128, 64): (5.89e9, "profiles/sddmm_kernel_c3_f128.md"),
-}
+def ncu_dram_traffic(workload: str, f: int, tile: int) -> tuple:
+    """(bytes, source) of dram__bytes_read.sum + dram__bytes_write.sum for one launch of the workload's
+    dominant kernel, from profiles/dram_traffic.json (written from the ncu captures summarised beside
+    it); (None, None) for a workload without a capture of the byte counters."""
+    try:
+        table = json.loads((ROOT / "profiles" / "dram_traffic.json").read_text())
+        entry = table[f"{workload}/f{f}/tile{tile}"]
+        return float(entry["dram_bytes_per_launch"]), entry["source"]
+    except (OSError, ValueError, KeyError):
+        return None, None
 
 
 # ------------------------------------------------------------------------------------------------
@@ -165,7 +166,7 @@ def cpu_spmm_sample(crow_cpu, col_cpu, val_cpu, x_cpu, target_nnz: int, repeats:
 
 # ------------------------------------------------------------------------------------------------
 def build_workload(name: str, f: int, device):
-    from autosage_b200 import synthetic as syn
+    from benchlib import synthetic as syn
 
     spec = {"c2_spmm": syn.REDDIT_LIKE, "c3_sddmm": syn.REDDIT_LIKE, "c4_attention": syn.ARXIV_LIKE,
             "c5_spmm": syn.PRODUCTS_LIKE}[name]
@@ -364,8 +365,8 @@ def run_ours_single(args) -> dict:
             "peak_source": f"{peak_kind} HBM copy bandwidth (burst)",
             "unit": "GB/s",
             "frac": round(achieved / peak, 4),
-            "traffic": NCU_DRAM_TRAFFIC.get((args.workload, f, tile), (None, None))[0],
-            "traffic_source": NCU_DRAM_TRAFFIC.get((args.workload, f, tile), (None, None))[1],
+            "traffic": ncu_dram_traffic(args.workload, f, tile)[0],
+            "traffic_source": ncu_dram_traffic(args.workload, f, tile)[1],
             "note": "achieved counts every gathered dense row (CSR + gathered rows + output); when the dense operand "
                     "fits the 126 MB L2 the gather is served by L2 and achieved exceeds the HBM peak",
             "launch_ms": round(launch_ms, 4),
@@ -436,27 +437,52 @@ def run_ours_single(args) -> dict:
     return line
 
 
+def conv_workload_label(n: int, nnz: int, f: int, out_f: int = 256) -> str:
+    """config.workload of the default benchmark; both arms print the same string."""
+    return (f"c5_conv: row-partitioned AutoSAGEConv forward, power-law CSR {n} rows, {nnz} nnz, "
+            f"F={f}, Linear {f}->{out_f}, unweighted")
+
+
+def reference_graph(args):
+    """The benchmark graph on the host.  With a GPU present it is generated there and copied back, which
+    gives exactly the arrays the GPU arm multiplies (same device generator, same seed); without one the
+    CPU generator draws the columns (same degrees, same distribution)."""
+    from benchlib import synthetic as syn
+
+    spec = syn.REDDIT_LIKE if not args.workload.startswith("c5") else syn.PRODUCTS_LIKE
+    if args.cpu_sample_nnz > 0:
+        # only the sampled rows are materialised: same degree sequence, columns iid uniform over all N
+        # columns and sorted inside each row
+        degree, _ = syn.powerlaw_degrees(spec.rows, spec.target_nnz, spec.alpha, spec.max_degree, 0)
+        crow = torch.zeros(spec.rows + 1, dtype=torch.long)
+        torch.cumsum(degree, 0, out=crow[1:])
+        rows = int(torch.searchsorted(crow, torch.tensor(args.cpu_sample_nnz)).clamp(1, spec.rows))
+        sub_crow, sub_col = syn.csr_from_degrees(degree[:rows], spec.rows, seed=0)
+        return spec, sub_crow, sub_col, int(degree.sum()), rows
+    device = torch.device("cuda", 0) if torch.cuda.is_available() else None
+    crow, col, info = syn.powerlaw_csr(spec, seed=0, device=device)
+    crow, col = crow.cpu(), col.cpu()
+    if device is not None:
+        torch.cuda.empty_cache()
+    return spec, crow, col, info["nnz"], spec.rows
+
+
 def run_reference(args) -> dict:
-    """The reference's CPU implementation of the path (torch.sparse.mm over a CSR tensor, as
-    restated in oracle/) on this host's cores; each step is one call on a bounded row sample."""
-    from autosage_b200 import synthetic as syn
+    """The reference's CPU implementation of the path (torch.sparse.mm over a CSR tensor, as restated
+    in oracle/, then nn.Linear for the layer workload) on all of this host's cores.  By default every
+    step is one call on the WHOLE graph of the GPU arm; --cpu-sample-nnz K (the in-line cpu_baseline leg
+    of the GPU arm uses it) restricts a step to the first rows holding about K edges, gathering from the
+    full X.  The reported time is the median of the timed steps."""
+    from benchlib import synthetic as syn
+    from oracle import oracle
 
     # torch.distributed.run exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host core
     torch.set_num_threads(max(1, os.cpu_count() or 1))
-    spec = syn.REDDIT_LIKE if not args.workload.startswith("c5") else syn.PRODUCTS_LIKE
-    # Only the sampled rows are materialised on the host: same degree sequence as the GPU arm's
-    # graph, columns iid uniform over all N columns and sorted inside each row.
-    degree, _ = syn.powerlaw_degrees(spec.rows, spec.target_nnz, spec.alpha, spec.max_degree, 0)
+    spec, sub_crow, sub_col, total_nnz, rows = reference_graph(args)
     n, f = spec.rows, args.features
-    info = {"rows": n, "nnz": int(degree.sum())}
-    weighted = not args.workload.startswith("c5")
-    from oracle import oracle
-
-    crow = torch.zeros(n + 1, dtype=torch.long)
-    torch.cumsum(degree, 0, out=crow[1:])
-    rows = int(torch.searchsorted(crow, torch.tensor(args.cpu_sample_nnz)).clamp(1, n))
-    sub_crow, sub_col = syn.csr_from_degrees(degree[:rows], n, seed=0)
     nnz = int(sub_crow[-1])
+    whole = rows == n
+    weighted = not args.workload.startswith("c5")
     sub_val = syn.edge_values(nnz, seed=0) if weighted else None
     x = syn.dense(n, f, 3)
     conv = args.workload == "c5_conv"  # the layer forward: aggregation, then Linear F -> 256
@@ -464,22 +490,32 @@ def run_reference(args) -> dict:
         torch.manual_seed(0)
         linear = torch.nn.Linear(f, 256)
         torch.nn.init.xavier_uniform_(linear.weight)
+        torch.nn.init.zeros_(linear.bias)
 
     def reference_step():
         aggregated = oracle.spmm_reference_cpu(sub_crow, sub_col, sub_val, x)
         return linear(aggregated) if conv else aggregated
 
+    laps = []
     with torch.no_grad():
         for _ in range(max(1, min(args.warmup, 2))):
             reference_step()
-        t0 = time.perf_counter()
         for _ in range(args.steps):
+            t0 = time.perf_counter()
             reference_step()
-        seconds = (time.perf_counter() - t0) / args.steps
+            laps.append(time.perf_counter() - t0)
+    seconds = statistics.median(laps)
     sample_bytes = spmm_bytes(rows, nnz, f, weighted) + (4 * rows * f + 4 * rows * 256 if conv else 0)
     value = round(sample_bytes / seconds / 1e9, 3)
-    sample = (f"first {rows} rows ({nnz} nnz) of the {info['rows']}-row CSR against the full X; "
-              f"torch.sparse.mm on CPU float32" + (", then nn.Linear on those rows" if conv else ""))
+    if whole:
+        sample = (f"the whole graph ({rows} rows, {nnz} nnz) per step; torch.sparse.mm on CPU float32"
+                  + (", then nn.Linear" if conv else "") + "; median of the timed steps")
+    else:
+        sample = (f"first {rows} rows ({nnz} nnz) of the {n}-row CSR against the full X; "
+                  f"torch.sparse.mm on CPU float32" + (", then nn.Linear on those rows" if conv else "")
+                  + "; median of the timed steps")
+    workload = conv_workload_label(n, total_nnz, f) if conv else (
+        f"{args.workload}: power-law CSR {n} rows, {total_nnz} nnz, F={f}" + (", weighted" if weighted else ""))
     return {
         "impl": "reference",
         "metric": "algorithmic_GBps",
@@ -489,13 +525,14 @@ def run_reference(args) -> dict:
         "steps": args.steps,
         "warmup": args.warmup,
         "ms_per_step": round(seconds * 1e3, 3),
+        "ms_per_step_mean_min_max": [round(statistics.fmean(laps) * 1e3, 3), round(min(laps) * 1e3, 3),
+                                     round(max(laps) * 1e3, 3)],
         "higher_is_better": True,
         "scaling": "strong",
         "vs_baseline": None,
         "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": f"{args.workload}: power-law CSR {n} rows, {info['nnz']} nnz, F={f}"
-                               + (", weighted" if weighted else ""), "sample": sample},
+        "config": {"workload": workload, "sample": sample},
         "edges_f_per_s": round(nnz * f / seconds, 1),
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
@@ -515,7 +552,9 @@ def main() -> None:
     parser.add_argument("--tile", type=int, default=None)
     parser.add_argument("--warps", type=int, default=4)
     parser.add_argument("--hub-threshold", type=int, default=1024)
-    parser.add_argument("--cpu-sample-nnz", type=int, default=4_000_000)
+    parser.add_argument("--cpu-sample-nnz", type=int, default=None,
+                        help="CPU legs: edges of the row sample one call covers (default: 4,000,000 for the "
+                             "in-line cpu_baseline of the GPU arm, 0 = the whole graph for --impl reference)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-other-configs", action="store_true",
                         help="N = 1: skip the short runs of configurations 2, 3 and 4")
@@ -539,12 +578,14 @@ def main() -> None:
         # resident; configuration 5's X is ten times L2 and whole 128-float rows stream best.
         args.tile = 128 if args.workload.startswith("c5") else 64
 
+    if args.cpu_sample_nnz is None:
+        args.cpu_sample_nnz = 0 if args.impl == "reference" else 4_000_000
     if args.impl == "reference":
         if rank == 0:
             print(json.dumps(run_reference(args)), flush=True)
         return
     if world > 1 or args.gpus > 1 or args.workload == "c5_conv":
-        from autosage_b200 import dist_bench
+        from benchlib import dist_bench
 
         line = dist_bench.run(args)
         if line is not None:

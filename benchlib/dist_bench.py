@@ -1,4 +1,4 @@
-"""Multi-GPU leg of bench.py: BASELINE configuration 5, the row-partitioned AutoSAGEConv forward.
+"""Sharded leg of bench.py: the row-partitioned AutoSAGEConv forward on the ogbn-products-sized graph.
 
 Launched by ``torch.distributed.run`` with one rank per GPU.  Every rank builds the same seeded
 graph on its own GPU, keeps its nnz-balanced row shard, and the timed step is: gather of X over
@@ -21,6 +21,53 @@ def conv_bytes(n_rows: int, nnz: int, f: int, out_f: int) -> int:
     spmm = 8 * (n_rows + 1) + 8 * nnz + 4 * nnz * f + 4 * n_rows * f
     linear = 4 * n_rows * f + 4 * n_rows * out_f
     return spmm + linear
+
+
+def bind_to_gpu_numa_node(local_rank: int) -> dict:
+    """Restrict this process to the CPUs of the NUMA node its GPU hangs off (read from sysfs), so that
+    the pinned host buffers allocated afterwards land in that node's memory.  With one process per GPU
+    started by torch.distributed.run nothing else decides where pinned pages go, and copies between a GPU
+    and the other socket's memory cross the inter-socket link.  Returns what it found and did."""
+    found = {"gpu_numa_node": None, "bound_cpus": None, "cpus_before": len(os.sched_getaffinity(0))}
+    try:
+        props = torch.cuda.get_device_properties(local_rank)
+        if hasattr(props, "pci_bus_id"):
+            address = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        else:
+            import pynvml
+
+            pynvml.nvmlInit()
+            raw = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(local_rank)).busId
+            address = (raw.decode() if isinstance(raw, bytes) else raw).lower()[-12:]
+        found["pci"] = address
+        node = int(open(f"/sys/bus/pci/devices/{address}/numa_node").read().strip())
+        found["gpu_numa_node"] = node
+        if node >= 0:
+            cpus = set()
+            for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+                first, _, last = part.partition("-")
+                cpus.update(range(int(first), int(last or first) + 1))
+            allowed = cpus & os.sched_getaffinity(0)
+            if allowed:
+                os.sched_setaffinity(0, allowed)
+                found["bound_cpus"] = len(allowed)
+    except (OSError, ValueError, ImportError, AttributeError, RuntimeError) as exc:
+        found["error"] = f"{type(exc).__name__}: {exc}"
+    return found
+
+
+def compare_with_single_gpu(single_rows, y_sharded, out_sharded, weight) -> tuple[float, float]:
+    """Worst error/bound of this rank's aggregated rows and layer outputs against the single-GPU run.
+    Both sides are float32 results that each lie within rtol 1e-5 / atol 1e-5*sqrt(degree) of the exact
+    value, so their difference may reach twice that; the layer's bound is the aggregation's carried
+    through |W| plus the projection's own rounding."""
+    y_single, out_single, root_degree = single_rows
+    bound_y = 2.0 * (1e-5 * y_single.double().abs() + 1e-5 * root_degree[:, None])
+    ratio_y = float(((y_sharded.double() - y_single.double()).abs() / bound_y).max()) if y_single.numel() else 0.0
+    carried = bound_y.float() @ weight.abs().t()
+    bound_out = carried.double() + 2.0 * (1e-5 * out_single.double().abs() + 1e-5 * weight.size(1) ** 0.5)
+    ratio_out = float(((out_sharded.double() - out_single.double()).abs() / bound_out).max()) if out_single.numel() else 0.0
+    return ratio_y, ratio_out
 
 
 def _single_gpu_extras(args, bench, shard, layer, algorithmic, n, nnz, f, out_f, device) -> dict:
@@ -84,7 +131,7 @@ def run(args):
     import bench  # the launcher script: clock sampler and peak lookup live there
     import autosage_b200
     from autosage_b200 import dist as asg_dist
-    from autosage_b200 import synthetic as syn
+    from benchlib import synthetic as syn
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -115,16 +162,29 @@ def run(args):
     bounds = asg_dist.partition_rows(crow, world)
     shard = asg_dist.shard_csr(crow, col, None, rank, world, bounds, groups=args.groups if args.groups else min(world, 4))
 
-    # The same layer on ONE GPU (no sharding, no exchange), timed inside this job so that every
-    # multi-GPU line carries its own strong-scaling reference.  Every rank times it on its own GPU
-    # at the same moment; the maximum over ranks is reported.
+    torch.manual_seed(0)
+    weight = torch.nn.init.xavier_uniform_(torch.empty(out_f, f, device=device))
+    bias = torch.zeros(out_f, device=device)
+    gen = torch.Generator(device=device).manual_seed(3)
+    x_all = torch.randn(n, f, generator=gen, device=device)  # same stream of numbers on every rank
+
+    def seeded(layer):
+        with torch.no_grad():
+            layer.linear.weight.copy_(weight)
+            layer.linear.bias.copy_(bias)
+        return layer
+
+    # The same layer on ONE GPU (no sharding, no exchange), same X and weights, run inside this job so
+    # that every multi-GPU line carries its own strong-scaling reference AND a result check: this rank's
+    # rows of the single-GPU aggregation and output are kept and compared with the sharded step below.
+    # Every rank times it on its own GPU at the same moment; the maximum over ranks is reported.
     single_ms = None
+    single_rows = None
     if multi:
-        torch.manual_seed(0)
         whole = asg_dist.shard_csr(crow, col, None, 0, 1, asg_dist.partition_rows(crow, 1))
-        solo = asg_dist.ShardedAutoSAGEConv(whole, f, out_f, bias=True, feature_tile=args.tile, warps=args.warps,
-                                            threshold=args.hub_threshold).to(device)
-        solo.spmm.x_local.normal_(generator=torch.Generator(device=device).manual_seed(3))
+        solo = seeded(asg_dist.ShardedAutoSAGEConv(whole, f, out_f, bias=True, feature_tile=args.tile, warps=args.warps,
+                                                   threshold=args.hub_threshold).to(device))
+        solo.spmm.x_local.copy_(x_all)
         with torch.no_grad():
             for _ in range(3):
                 solo()
@@ -136,19 +196,18 @@ def run(args):
                 solo()
             t1.record()
             torch.cuda.synchronize()
+            lo, hi = shard.row_begin, shard.row_end
+            single_rows = (solo.spmm.forward()[lo:hi].clone(), solo()[lo:hi].clone(),
+                           (crow[lo + 1:hi + 1] - crow[lo:hi]).clamp_min(1).double().sqrt())
         single_ms = float(reduce_max(torch.tensor([t0.elapsed_time(t1) / reps], device=device)).item())
         del solo, whole
     del crow, col
     torch.cuda.empty_cache()
 
-    torch.manual_seed(0)
-    layer = asg_dist.ShardedAutoSAGEConv(shard, f, out_f, bias=True, feature_tile=args.tile, warps=args.warps,
-                                         threshold=args.hub_threshold, exchange=args.exchange,
-                                         copy_streams=args.copy_streams, slabs=args.slabs).to(device)
-    torch.nn.init.xavier_uniform_(layer.linear.weight)
-    torch.nn.init.zeros_(layer.linear.bias)
-    gen = torch.Generator(device=device).manual_seed(3)
-    x_all = torch.randn(n, f, generator=gen, device=device)  # same stream of numbers on every rank
+    layer = seeded(asg_dist.ShardedAutoSAGEConv(shard, f, out_f, bias=True, feature_tile=args.tile, warps=args.warps,
+                                                threshold=args.hub_threshold, exchange=args.exchange,
+                                                copy_streams=args.copy_streams, slabs=args.slabs).to(device))
+    pinning = bind_to_gpu_numa_node(local_rank) if multi else None  # before any pinned buffer is allocated
     x_shard_host = x_all[shard.row_begin:shard.row_end].cpu().pin_memory()
     layer.spmm.x_local.copy_(x_all[shard.row_begin:shard.row_end])
     del x_all
@@ -185,11 +244,14 @@ def run(args):
     torch.cuda.synchronize()
     barrier()
     torch.cuda.synchronize()
+    step_marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     with sampler as clocks:
         host_begin = time.perf_counter()
         begin.record(stream)
-        for _ in range(args.steps):
+        step_marks[0].record(stream)
+        for i in range(args.steps):
             step()
+            step_marks[i + 1].record(stream)
         end.record(stream)
         host_enqueue_ms = (time.perf_counter() - host_begin) * 1e3 / args.steps
         torch.cuda.synchronize()
@@ -197,6 +259,10 @@ def run(args):
         torch.cuda.synchronize()
     elapsed = reduce_max(torch.tensor([begin.elapsed_time(end)], device=device))
     ms_per_step = float(elapsed.item()) / args.steps
+    # per step: the slowest rank's time; then median / min / max over the steps
+    per_step = reduce_max(torch.tensor([step_marks[i].elapsed_time(step_marks[i + 1]) for i in range(args.steps)],
+                                       device=device)).cpu().tolist()
+    ms_median = statistics.median(per_step)
     spmm_launch_ms = [a.elapsed_time(b) for a, b in spmm_events]
     spmm_events.clear()
 
@@ -244,6 +310,18 @@ def run(args):
         stacked = torch.stack(everyone).cpu()
         order = sorted(range(len(names)), key=lambda i: float(stacked[:, i].max()))
         timeline = {names[i]: [round(float(stacked[:, i].min()), 3), round(float(stacked[:, i].max()), 3)] for i in order}
+
+    # result check: this rank's rows of the sharded step against the single-GPU layer of the same job
+    parity = None
+    if multi and single_rows is not None:
+        with torch.no_grad():
+            ratios = compare_with_single_gpu(single_rows, layer.spmm.forward(), step(), weight)
+        worst = reduce_max(torch.tensor(list(ratios), device=device)).cpu().tolist()
+        parity = {"aggregated_rows_worst_error_over_bound": round(worst[0], 4),
+                  "layer_output_worst_error_over_bound": round(worst[1], 4),
+                  "rule": "|sharded - single| <= 2*(1e-5*|single| + 1e-5*sqrt(row degree)), carried through |W| for the output"}
+        single_rows = None
+        torch.cuda.empty_cache()
 
     aggregated_scratch = torch.empty(shard.n_local, f, device=device)
     with torch.no_grad():
@@ -305,6 +383,33 @@ def run(args):
 
     e2e_serial_ms = time_e2e(lambda k: [e2e_serial_step() for _ in range(k)])
     e2e_ms = time_e2e(lambda k: [e2e_streamed_step(i) for i in range(k)])
+    # the two PCIe directions alone, all ranks copying at once: per-rank GB/s, slowest and fastest rank
+    def copy_rate(fn, nbytes):
+        fn()
+        torch.cuda.synchronize()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(3):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        barrier()
+        rate = torch.tensor([nbytes * 3 / (a.elapsed_time(b) * 1e-3) / 1e9], device=device)
+        if not multi:
+            return [round(float(rate.item()), 2)] * 2
+        rates = [torch.zeros_like(rate) for _ in range(world)]
+        dist.all_gather(rates, rate)
+        flat = [float(r.item()) for r in rates]
+        return [round(min(flat), 2), round(max(flat), 2)]
+
+    last_out = step()
+    pcie = {
+        "h2d_GBps_per_rank_min_max": copy_rate(lambda: layer.spmm.x_local.copy_(x_shard_host, non_blocking=True),
+                                               x_shard_host.numel() * 4),
+        "d2h_GBps_per_rank_min_max": copy_rate(lambda: out_host.copy_(last_out, non_blocking=True), out_host.numel() * 4),
+        "numa": pinning,
+    }
     io_bytes = torch.tensor([x_shard_host.numel() * 4, out_host.numel() * 4], device=device, dtype=torch.long)
     local_nnz = torch.tensor([shard.col.numel()], device=device, dtype=torch.long)
     gathered = [torch.zeros_like(local_nnz) for _ in range(world)]
@@ -332,7 +437,7 @@ def run(args):
         spmm_algorithmic = bench.spmm_bytes(n, nnz, f, False)
         launch_ms = statistics.fmean(spmm_launch_ms)
         achieved = spmm_algorithmic / (launch_ms * 1e-3) / 1e9
-        traffic, traffic_source = bench.NCU_DRAM_TRAFFIC.get(("c5_spmm", f, args.tile), (None, None))
+        traffic, traffic_source = bench.ncu_dram_traffic("c5_spmm", f, args.tile)
         roofline = {
             "bound": "hbm",
             "kernel": "spmm_kernel_deep + spmm_short_kernel (the aggregation; %.0f %% of the step)"
@@ -361,14 +466,15 @@ def run(args):
             "steps": args.steps,
             "warmup": max(args.warmup, 3),
             "ms_per_step": round(ms_per_step, 4),
+            "ms_per_step_median_min_max": [round(ms_median, 4), round(min(per_step), 4), round(max(per_step), 4)],
+            "value_at_median": round(algorithmic / (ms_median * 1e-3) / 1e9, 2),
             "higher_is_better": True,
             "scaling": "strong",
             "vs_baseline": None,
             "dtype": "f32",
             "data": "synthetic",
             "config": {
-                "workload": f"c5_conv: row-partitioned AutoSAGEConv forward, power-law CSR {n} rows, {nnz} nnz, "
-                            f"F={f}, Linear {f}->{out_f}, unweighted",
+                "workload": bench.conv_workload_label(n, nnz, f, out_f),
                 "parallelism": f"rows sharded by nnz over {world} GPUs; X gathered over NVLink "
                                f"({'copy-engine pulls from peer memory' if layer.spmm.exchange == 'peer' else 'NCCL send/recv steps'}), "
                                f"overlapped with {len(shard.blocks)} column-block SpMMs per GPU",
@@ -387,6 +493,10 @@ def run(args):
             "host_enqueue_ms_per_step": round(host_enqueue_ms, 4),
             # [earliest rank, latest rank] offset of each mark from its rank's step start
             "timeline_ms_min_max_over_ranks": timeline,
+            "parity_vs_single_gpu": None if parity is None else (
+                "ok" if max(parity["aggregated_rows_worst_error_over_bound"],
+                            parity["layer_output_worst_error_over_bound"]) <= 1.0 else "FAILED"),
+            "parity_detail": parity,
             "single_gpu_ms_per_step": None if single_ms is None else round(single_ms, 4),
             "speedup_vs_1gpu_same_workload": None if single_ms is None else round(single_ms / ms_per_step, 3),
             "roofline": roofline,
@@ -401,6 +511,7 @@ def run(args):
                         "(second stream, two pinned output buffers); every step's input and output cross PCIe "
                         "inside the timed region",
             },
+            "e2e_pcie": pcie,
             "e2e_serial": {
                 "value": round(algorithmic / (e2e_serial_ms * 1e-3) / 1e9, 2),
                 "unit": "GB/s",

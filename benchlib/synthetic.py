@@ -30,7 +30,7 @@ class GraphSpec:
     max_degree: int
 
 
-# BASELINE configurations 2-5
+# the benchmark graphs: stand-ins for Reddit, ogbn-arxiv and ogbn-products
 REDDIT_LIKE = GraphSpec("powerlaw-232965", 232_965, 114_615_892, 2.1, 21_657)
 ARXIV_LIKE = GraphSpec("powerlaw-169343", 169_343, 2_480_000, 2.2, 13_000)
 PRODUCTS_LIKE = GraphSpec("powerlaw-2449029", 2_449_029, 123_718_280, 2.0, 17_500)
@@ -96,7 +96,7 @@ def powerlaw_csr(spec: GraphSpec, seed: int = 0, device: Optional[torch.device] 
 
 
 def uniform_degree_csr(rows: int, max_degree: int = 32, seed: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
-    """BASELINE configuration 1: degree uniform in [1, max_degree], distinct uniform columns."""
+    """The small CPU-runnable benchmark graph: degree uniform in [1, max_degree], distinct uniform columns."""
     gen = torch.Generator().manual_seed(seed)
     degree = torch.randint(1, max_degree + 1, (rows,), generator=gen)
     crow = torch.zeros(rows + 1, dtype=torch.long)

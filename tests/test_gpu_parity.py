@@ -316,10 +316,10 @@ def test_kernels_match_reference_outputs(lib, orc, golden, case):
 
 # ------------------------------------------------------------------------- size-independent checks
 def test_full_size_spmm_properties():
-    """BASELINE configuration 2 at full size (232,965 rows, ~114.6 M nnz): properties that need no
+    """The Reddit-sized graph at full size (232,965 rows, ~114.6 M nnz): properties that need no
     oracle run. With X = ones, Y[i, :] is the sum of the row's weights; SpMM is linear in X."""
     import autosage_b200
-    from autosage_b200 import synthetic as syn
+    from benchlib import synthetic as syn
 
     assert autosage_b200.load_native()
     dev = torch.device("cuda")
@@ -350,10 +350,10 @@ def test_full_size_spmm_properties():
 
 
 def test_full_size_attention_properties():
-    """BASELINE configuration 4 (169,343 rows, ~2.48 M nnz, F = 128): with V constant per column the
+    """The ogbn-arxiv-sized graph (169,343 rows, ~2.48 M nnz, F = 128): with V constant per column the
     output of a softmax-weighted average is that constant; fused equals the three-pass pipeline."""
     import autosage_b200
-    from autosage_b200 import synthetic as syn
+    from benchlib import synthetic as syn
 
     dev = torch.device("cuda")
     crow, col, info = syn.powerlaw_csr(syn.ARXIV_LIKE, device=dev)

@@ -296,6 +296,24 @@ def test_operators_replay_inside_a_cuda_graph(asg, orc):
     exact_s = orc.sddmm(to_np(crow), to_np(col), q_d.cpu().numpy(), k_d.cpu().numpy())
     ok, ratio = orc.within_tolerance(s.cpu().numpy(), exact_s, to_np(crow), per_edge=True)
     assert ok, ratio
+    # The captured launches must not lean on the plan cache: evict every cached plan, let the freed
+    # memory be recycled by other tensors, and replay once more.
+    from autosage_b200 import _native
+
+    _native.clear_plan_cache()
+    torch.cuda.empty_cache()
+    junk = [torch.full((1 << 20,), 0x7fffffff, device="cuda", dtype=torch.int32) for _ in range(16)]
+    for other in range(20):  # more probe-sized entries than the cache holds
+        other_crow = torch.arange(0, 5 * (300 + other) + 1, 5, device="cuda")
+        torch.ops.autosage.spmm_csr(other_crow, torch.zeros(5 * (300 + other), dtype=torch.long, device="cuda"), None,
+                                    torch.ones(300 + other, 8, device="cuda"))
+    x_d.copy_(dense(4000, 64, 20))
+    graph.replay()
+    torch.cuda.synchronize()
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), x_d.cpu().numpy())
+    ok, ratio = orc.within_tolerance(y.cpu().numpy(), exact, to_np(crow))
+    assert ok, ratio
+    del junk
 
 
 def test_debug_index_check(monkeypatch):
@@ -316,7 +334,7 @@ def test_debug_index_check(monkeypatch):
 def test_probe_on_row_sample_prefers_the_kernels(asg, isolated_cache, monkeypatch):
     """On a power-law graph the whole-row probe sample ranks the kernels ahead of the gather-dot
     baseline (SDDMM) and records a full-graph candidate; the induced sample stays selectable."""
-    from autosage_b200 import synthetic as syn
+    from benchlib import synthetic as syn
 
     dev = torch.device("cuda")
     crow, col, info = syn.powerlaw_csr(syn.ARXIV_LIKE, seed=0, device=dev)

@@ -287,6 +287,24 @@ def test_edge_index_to_csr_is_bit_exact(golden):
         edge_index_to_csr(edge_index, 40, rows_by="both")
     crow, col = edge_index_to_csr(torch.zeros(2, 0, dtype=torch.long), 3)
     assert crow.tolist() == [0, 0, 0, 0] and col.numel() == 0
+    # a row id outside [0, num_nodes) is an error (the reference's index_add_ raises IndexError on the CPU)
+    with pytest.raises(IndexError):
+        edge_index_to_csr(torch.tensor([[0, 1], [1, 5]]), 4)
+    with pytest.raises((IndexError, RuntimeError)):
+        edge_index_to_csr(torch.tensor([[0, 1], [1, -1]]), 4)
+
+
+def test_layer_pickles_after_a_forward():
+    """The CSR memo holds a weak reference; a layer must still pickle / deepcopy after it has run."""
+    import copy
+    import pickle
+
+    torch.manual_seed(1)
+    layer = asg.AutoSAGEConv(3, 2)
+    x, edge_index = torch.randn(4, 3), torch.tensor([[0, 1, 2, 3], [1, 2, 3, 0]])
+    expected = layer(x, edge_index)
+    for clone in (pickle.loads(pickle.dumps(layer)), copy.deepcopy(layer)):
+        assert torch.equal(clone(x, edge_index), expected)
 
 
 def test_convolution_shapes_info_and_weight_order():
