@@ -51,6 +51,9 @@ SIGNATURES = {
     "asg_csr_build_workspace_bytes": (_SZ, [_I64, _I64]),
     "asg_csr_from_edges": (_INT, [_P, _P, _P, _I64, _I64, _P, _P, _P, _P, _P, _SZ, _P]),
     "asg_linear_bias": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _P]),
+    "asg_linear_workspace_bytes": (_SZ, [_I64, _I64]),
+    "asg_linear_supported": (_INT, [_I64, _I64]),
+    "asg_linear_bias_umma": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
     "asg_copy_2d": (_INT, [_P, _SZ, _P, _SZ, _SZ, _SZ, _P]),
     "asg_workspace_status": (_INT, [_P, _P, _P]),
     "asg_spmm_csr_split_noalloc": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _P]),
@@ -332,6 +335,23 @@ def linear_bias(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
     """out = x @ weight^T + bias on the tensor cores at float32 accuracy (contiguous float32 CUDA tensors)."""
     check(library().asg_linear_bias(x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(),
                                     out.data_ptr(), x.size(0), x.size(1), weight.size(0), _stream(x.device)))
+
+
+def linear_umma_supported(in_features: int, out_features: int) -> bool:
+    return bool(library().asg_linear_supported(int(in_features), int(out_features)))
+
+
+def linear_bias_umma(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                     workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = x @ weight^T + bias from the hand-written tcgen05 kernel; returns the workspace used (its
+    header carries the kernel's status word)."""
+    if workspace is None:
+        workspace = torch.empty(int(library().asg_linear_workspace_bytes(x.size(1), weight.size(0))), dtype=torch.uint8,
+                                device=x.device)
+    check(library().asg_linear_bias_umma(x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(),
+                                         out.data_ptr(), x.size(0), x.size(1), weight.size(0), workspace.data_ptr(),
+                                         workspace.numel(), _stream(x.device)))
+    return workspace
 
 
 def workspace_status(workspace: torch.Tensor) -> int:

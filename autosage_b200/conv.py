@@ -37,8 +37,10 @@ def apply_linear(linear: nn.Linear, aggregated: torch.Tensor) -> torch.Tensor:
 
     CUDA float32, no gradient wanted: the library's tensor-core Linear (float32 operands split into
     three bfloat16 pieces each, piece products summed in float32, bias in the epilogue).  It keeps
-    float32 accuracy - no TF32 rounding - and measured 1.5 ms against 3.3 ms (cuBLAS SGEMM) + bias
-    pass at 2.45 M x 128 -> 256 on B200.  ``AUTOSAGE_LINEAR=cublas`` selects the cuBLAS route below.
+    float32 accuracy - no TF32 rounding.  in_features a multiple of 64 and out_features a multiple of
+    32 up to 256 run the hand-written tcgen05 kernel (1.05 ms at 2.45 M x 128 -> 256 on B200), other
+    sizes the CUTLASS instantiation (1.5 ms there; ``AUTOSAGE_LINEAR_KERNEL=cutlass`` forces it); cuBLAS
+    SGEMM plus a bias pass takes 3.3 ms.  ``AUTOSAGE_LINEAR=cublas`` selects the cuBLAS route below.
 
     Otherwise on CUDA float32 the product and the bias are issued separately (matmul, then an in-place
     add): cuBLAS's fused-bias SGEMM measured twice as slow as the plain one at these shapes (6.1 ms
@@ -52,7 +54,12 @@ def apply_linear(linear: nn.Linear, aggregated: torch.Tensor) -> torch.Tensor:
             x = aggregated if aggregated.is_contiguous() else aggregated.contiguous()
             out = torch.empty(x.size(0), linear.out_features, dtype=torch.float32, device=x.device)
             bias = None if linear.bias is None else linear.bias.detach().contiguous()
-            _native.linear_bias(x.detach(), linear.weight.detach().contiguous(), bias, out)
+            weight = linear.weight.detach().contiguous()
+            if (os.getenv("AUTOSAGE_LINEAR_KERNEL", "umma") == "umma"
+                    and _native.linear_umma_supported(x.size(1), linear.out_features)):
+                _native.linear_bias_umma(x.detach(), weight, bias, out)   # the hand-written tcgen05 kernel
+            else:
+                _native.linear_bias(x.detach(), weight, bias, out)        # other sizes: the CUTLASS instantiation
             return out
         out = torch.mm(aggregated, linear.weight.t())
         if linear.bias is None:

@@ -187,6 +187,22 @@ int asg_linear_bias(const float* x, const float* weight, const float* bias, floa
                     int64_t in_features, int64_t out_features, void* stream);
 
 /*
+ * The same product as asg_linear_bias from the hand-written tcgen05 kernel (csrc/asg_linear_umma.cu):
+ * persistent CTAs, x split into bfloat16 pieces on the fly, the weight split once per call into the
+ * workspace, accumulators in tensor memory, bias in the epilogue.  Replaces the nn.Linear call of
+ * autosage/conv.py:55 for the sizes asg_linear_supported() accepts: in_features a multiple of 64,
+ * out_features a multiple of 32 up to 256.  x and out 16-byte aligned, dense row-major.
+ * The workspace holds asg_linear_workspace_bytes(in_features, out_features) bytes, 256-byte aligned; its
+ * first 256 bytes are a header whose status word asg_workspace_status() reads (non-zero: a bounded wait
+ * inside the kernel gave up and the output is invalid).
+ */
+size_t asg_linear_workspace_bytes(int64_t in_features, int64_t out_features);
+int asg_linear_supported(int64_t in_features, int64_t out_features);
+int asg_linear_bias_umma(const float* x, const float* weight, const float* bias, float* out, int64_t rows,
+                         int64_t in_features, int64_t out_features, void* workspace, size_t workspace_bytes,
+                         void* stream);
+
+/*
  * Pitched device-to-device copy of `height` rows of `width_bytes` bytes (cudaMemcpy2DAsync; runs on
  * the copy engines).  Either pointer may be peer-mapped memory of another GPU.
  */

@@ -487,6 +487,53 @@ def test_linear_bias_matches_float64(lib, rows, k, n, with_bias):
         assert float(err.max()) <= 2.0 * float((library.double() - exact).abs().max()) + 1e-7
 
 
+@pytest.mark.parametrize("rows,k,n,with_bias", [(1, 128, 256, True), (127, 128, 256, True), (128, 64, 32, True),
+                                                 (129, 64, 32, False), (1000, 128, 64, True), (5000, 256, 256, True),
+                                                 (70001, 192, 96, True), (0, 128, 256, True)])
+def test_linear_bias_umma_matches_float64(lib, rows, k, n, with_bias):
+    """The hand-written tcgen05 Linear: rtol 1e-5, atol 1e-5 * sqrt(in_features) against float64, rows
+    past the last full 128-row tile untouched, status word clear."""
+    dev = torch.device("cuda")
+    gen = torch.Generator().manual_seed(rows * 7 + k + n)
+    x = torch.randn(rows, k, generator=gen).to(dev)
+    weight = (torch.randn(n, k, generator=gen) / k ** 0.5).to(dev)
+    bias = torch.randn(n, generator=gen).to(dev) if with_bias else None
+    guard_rows = 3
+    whole = torch.full((rows + guard_rows, n), float("nan"), device=dev)
+    out = whole[:rows]
+    ws = lib.linear_bias_umma(x, weight, bias, out)
+    torch.cuda.synchronize()
+    if rows:
+        assert lib.workspace_status(ws) == 0
+    assert bool(torch.isnan(whole[rows:]).all())          # nothing written past the last row
+    exact = x.double() @ weight.double().t()
+    if with_bias:
+        exact = exact + bias.double()
+    if rows:
+        err = (out.double() - exact).abs()
+        bound = 1e-5 * exact.abs() + 1e-5 * k ** 0.5
+        # all six piece products go into one tensor-memory accumulator (the tensor core truncates each
+        # accumulation), which costs a few more ulps than cuBLAS SGEMM: still a quarter of the bound
+        assert bool((err <= 0.25 * bound).all()), float((err / bound).max())
+    # a second call with the same workspace and different operands (the ring phases start afresh)
+    if rows:
+        x2 = torch.randn(rows, k, generator=gen).to(dev)
+        lib.linear_bias_umma(x2, weight, bias, out, ws)
+        exact2 = x2.double() @ weight.double().t() + (bias.double() if with_bias else 0)
+        err2 = (out.double() - exact2).abs()
+        assert bool((err2 <= 1e-5 * exact2.abs() + 1e-5 * k ** 0.5).all())
+
+
+def test_linear_bias_umma_rejects_other_sizes(lib):
+    dev = torch.device("cuda")
+    assert lib.linear_umma_supported(128, 256) and lib.linear_umma_supported(64, 32)
+    assert not lib.linear_umma_supported(100, 256) and not lib.linear_umma_supported(128, 36)
+    assert not lib.linear_umma_supported(128, 512)
+    x, weight, out = torch.zeros(8, 100, device=dev), torch.zeros(36, 100, device=dev), torch.zeros(8, 36, device=dev)
+    with pytest.raises(RuntimeError, match="multiples of 64"):
+        lib.linear_bias_umma(x, weight, None, out)
+
+
 def test_linear_bias_rejects_unaligned_sizes(lib):
     dev = torch.device("cuda")
     x, weight, out = torch.zeros(8, 6, device=dev), torch.zeros(4, 6, device=dev), torch.zeros(8, 4, device=dev)
@@ -507,6 +554,12 @@ def test_layer_linear_uses_tensor_core_path(lib, monkeypatch):
         monkeypatch.setenv("AUTOSAGE_LINEAR", "cublas")
         plain = conv.apply_linear(linear, x)
     assert torch.allclose(fast, plain, rtol=1e-5, atol=1e-5 * 128 ** 0.5)
+    monkeypatch.delenv("AUTOSAGE_LINEAR")
+    monkeypatch.setenv("AUTOSAGE_LINEAR_KERNEL", "cutlass")
+    with torch.no_grad():
+        other = conv.apply_linear(linear, x.detach())
+    assert torch.allclose(fast, other, rtol=1e-5, atol=1e-5 * 128 ** 0.5)
+    monkeypatch.delenv("AUTOSAGE_LINEAR_KERNEL")
     y = conv.apply_linear(linear, x.requires_grad_())          # gradient wanted: differentiable route
     y.sum().backward()
     assert x.grad is not None and linear.weight.grad is not None
