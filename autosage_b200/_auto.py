@@ -11,7 +11,7 @@ by a hub row, threshold = degree from which a row takes the CTA-per-hub path).
 Deliberate departures, all invisible in the dict layout:
   * the probe runs on a seeded ROW sample that keeps every edge of a sampled row and gathers from
     the full dense operand, sized by WORK: the row fraction is raised from ``probe_fraction`` until
-    the sample holds about AUTOSAGE_PROBE_EDGES edges (default 32 M, roughly a millisecond of B200
+    the sample holds about AUTOSAGE_PROBE_EDGES edges (default 16 M, roughly half a millisecond of B200
     time; graphs below that are probed whole, without copying anything), and the candidates' time
     budget is the larger of ``probe_cap_ms`` and ``probe_iterations`` baseline runs.  The reference
     probes the sub-graph INDUCED by 3 % of the rows (``_auto.py:95-154``), which keeps ~0.1 % of the
@@ -89,6 +89,41 @@ def _time_cuda(function: Callable[[], torch.Tensor], *, warmup: int, iterations:
 
 def _without_output(timing: dict[str, Any]) -> dict[str, Any]:
     return {k: v for k, v in timing.items() if k != "output"}
+
+
+@torch.no_grad()
+def _time_cuda_batch(functions: list[Callable[[], torch.Tensor]], *, warmup: int, iterations: int) -> list[dict[str, Any]]:
+    """CUDA-event timing of several functions enqueued back to back: per function ``warmup`` untimed
+    calls and ``iterations`` timed ones, every lap between its own pair of events, ONE host
+    synchronisation after the last function.  (``_time_cuda`` synchronises after every lap, which the
+    reference does per candidate, ``autosage/_auto.py:324-378``.)"""
+    t0 = time.perf_counter()
+    recorded: list[list[tuple]] = []
+    for function in functions:
+        for _ in range(max(warmup, 0)):
+            function()
+        pairs = []
+        for _ in range(max(iterations, 1)):
+            begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            function()
+            finish.record()
+            pairs.append((begin, finish))
+        recorded.append(pairs)
+    torch.cuda.synchronize()
+    wall_each = (time.perf_counter() - t0) * 1000.0 / max(len(functions), 1)
+    timings = []
+    for pairs in recorded:
+        laps = [float(begin.elapsed_time(finish)) for begin, finish in pairs]
+        timings.append({
+            "best_ms": min(laps),
+            "mean_ms": statistics.fmean(laps),
+            "std_ms": statistics.pstdev(laps) if len(laps) > 1 else 0.0,
+            "iterations": len(laps),
+            "total_ms": sum(laps),
+            "wall_ms": wall_each,
+        })
+    return timings
 
 
 # ------------------------------------------------------------------------------------------------
@@ -192,6 +227,45 @@ class _ProbeSample:
     @property
     def rows(self) -> int:
         return self.crow.numel() - 1
+
+    # What the vendor baselines (which need exactly sized arrays) run on, and the numbers reported.
+    def exact(self):
+        return self.crow, self.col, self.val
+
+    def exact_rows(self, row_operand: torch.Tensor) -> torch.Tensor:
+        return row_operand
+
+    def counts(self) -> tuple[int, int]:
+        return self.rows, self.col.numel()
+
+
+class _DeviceRowSample(_ProbeSample):
+    """Row sample cut by the library (``asg_csr_row_sample``) without a host synchronisation.
+
+    ``crow`` / ``col`` / ``val`` are the arrays as allocated: a valid CSR of all selected rows over a
+    column array of ``capacity`` entries, of which the first ``kept[1]`` are meaningful (selected rows
+    that did not fit the capacity are empty).  The library's kernels run on them as they are; whoever
+    needs exactly sized arrays (cuSPARSE through torch, the reported counts) calls ``exact()``, which
+    reads the two counters back - by then the candidates have been timed and the stream is idle."""
+
+    def __init__(self, crow, col, val, selected, kept) -> None:
+        super().__init__(crow, col, val, selected, False, None)
+        self._kept = kept
+        self._counts: Optional[tuple[int, int]] = None
+
+    def counts(self) -> tuple[int, int]:
+        if self._counts is None:
+            rows_kept, edges_kept = (int(v) for v in self._kept.tolist())
+            self._counts = (rows_kept, edges_kept)
+        return self._counts
+
+    def exact(self):
+        rows_kept, edges_kept = self.counts()
+        return (self.crow[: rows_kept + 1], self.col[:edges_kept],
+                None if self.val is None else self.val[:edges_kept])
+
+    def exact_rows(self, row_operand: torch.Tensor) -> torch.Tensor:
+        return row_operand[: self.counts()[0]]
 
 
 def _probe_sample_kind() -> str:
@@ -365,46 +439,59 @@ def _probe_and_choose(
     graph: dict[str, Any],
     cache: ScheduleCache,
     sample_ms: float,
-    probe_rows: int,
-    probe_nonzeros: int,
-    baseline: Callable[[], torch.Tensor],
-    baseline_name: str,
+    sample: _ProbeSample,
+    make_baseline: Callable[[], tuple[Callable[[], torch.Tensor], str]],
     candidates: list[tuple[list[int], Callable[[], torch.Tensor]]],
     fallback: Optional[Callable[[], torch.Tensor]],
     verbose: bool,
     preferred: Optional[tuple] = None,
 ) -> dict[str, Any]:
-    """Times the baseline and the shortlisted candidates on the sample under the probe budget and
-    applies the guardrail.  ``candidates`` pairs the full-graph parameter list stored in the
-    schedule with a closure running it on the sample; ``fallback`` is the parameter-free native
-    kernel used when hub splitting is disabled."""
+    """Times the shortlisted candidates and the baseline on the sample and applies the guardrail.
+    ``candidates`` pairs the full-graph parameter list stored in the schedule with a closure running it
+    on the sample; ``fallback`` is the parameter-free native kernel used when hub splitting is disabled;
+    ``make_baseline`` builds the vendor baseline on the sample's exactly sized arrays.
+
+    Work-sized samples (the default): every candidate is enqueued back to back - one warm-up and two
+    timed laps each, every lap between its own events - with a single synchronisation after the last
+    one; only then are the sample's sizes read back, the baseline built and timed.  The induced sample
+    (AUTOSAGE_PROBE_SAMPLE=induced) keeps the reference's procedure: baseline first, then candidate after
+    candidate under ``probe_cap_ms``, synchronising after every lap."""
     work_sized = _probe_sample_kind() != "induced"
-    # work-sized samples: a slow baseline (the gather-dot SDDMM takes tens of ms) is not timed 7 times
-    base = _time_cuda(baseline, warmup=1, iterations=config.probe_iterations, cap_ms=25.0 if work_sized else None)
     timings: list[dict[str, Any]] = []
     best, best_params = _INF, None
-    remaining = config.probe_cap_ms
     if work_sized:
-        # ... and the candidates together may take as long as seven baseline runs
-        remaining = max(remaining, config.probe_iterations * base["best_ms"])
-    if candidates:
-        for index, (params, run) in enumerate(candidates):
-            if index > 0 and remaining <= 0.0:
-                break
-            lap = _time_cuda(run, warmup=1, iterations=config.probe_iterations, cap_ms=max(0.0, remaining))
-            remaining = max(0.0, remaining - lap["total_ms"])
-            timings.append({"candidate": list(params), **_without_output(lap)})
+        laps_each = max(1, min(2, config.probe_iterations))
+        runs = list(candidates) if candidates else ([(None, fallback)] if fallback is not None else [])
+        for (params, _), lap in zip(runs, _time_cuda_batch([run for _, run in runs], warmup=1, iterations=laps_each)):
+            timings.append({"candidate": None if params is None else list(params), **lap})
             if lap["best_ms"] < best:
-                best, best_params = lap["best_ms"], list(params)
-        if preferred is not None:
-            # a candidate within 5 % of the best is a tie on a sample: keep the library default then
-            for entry in timings:
-                if entry["candidate"] == list(preferred) and entry["best_ms"] <= 1.05 * best:
-                    best, best_params = entry["best_ms"], list(preferred)
-    elif fallback is not None:
-        lap = _time_cuda(fallback, warmup=1, iterations=config.probe_iterations, cap_ms=config.probe_cap_ms)
-        best = lap["best_ms"]
-        timings.append({"candidate": None, **_without_output(lap)})
+                best, best_params = lap["best_ms"], None if params is None else list(params)
+        baseline, baseline_name = make_baseline()
+        # a slow baseline (the gather-dot SDDMM takes tens of ms) is not timed three times
+        base = _time_cuda(baseline, warmup=1, iterations=laps_each, cap_ms=25.0)
+    else:
+        baseline, baseline_name = make_baseline()
+        base = _time_cuda(baseline, warmup=1, iterations=config.probe_iterations)
+        remaining = config.probe_cap_ms
+        if candidates:
+            for index, (params, run) in enumerate(candidates):
+                if index > 0 and remaining <= 0.0:
+                    break
+                lap = _time_cuda(run, warmup=1, iterations=config.probe_iterations, cap_ms=max(0.0, remaining))
+                remaining = max(0.0, remaining - lap["total_ms"])
+                timings.append({"candidate": list(params), **_without_output(lap)})
+                if lap["best_ms"] < best:
+                    best, best_params = lap["best_ms"], list(params)
+        elif fallback is not None:
+            lap = _time_cuda(fallback, warmup=1, iterations=config.probe_iterations, cap_ms=config.probe_cap_ms)
+            best = lap["best_ms"]
+            timings.append({"candidate": None, **_without_output(lap)})
+    if candidates and preferred is not None:
+        # a candidate within 5 % of the best is a tie on a sample: keep the library default then
+        for entry in timings:
+            if entry["candidate"] == list(preferred) and entry["best_ms"] <= 1.05 * best:
+                best, best_params = entry["best_ms"], list(preferred)
+    probe_rows, probe_nonzeros = sample.counts()
 
     enough = probe_rows >= config.minimum_probe_rows and probe_nonzeros >= config.minimum_probe_nonzeros
     wins = enough and best <= config.guardrail * base["best_ms"]
@@ -452,9 +539,9 @@ def _lookup(cache: ScheduleCache, config: SchedulerConfig, device, graph, op_nam
 
 def _probe_target_edges() -> int:
     try:
-        return max(1, int(os.getenv("AUTOSAGE_PROBE_EDGES", str(32 * 1024 * 1024))))
+        return max(1, int(os.getenv("AUTOSAGE_PROBE_EDGES", str(16 * 1024 * 1024))))
     except ValueError:
-        return 32 * 1024 * 1024
+        return 16 * 1024 * 1024
 
 
 class _WholeGraph(_ProbeSample):
@@ -468,9 +555,10 @@ class _WholeGraph(_ProbeSample):
 
 
 def _timed_sample(crow, col, val, config: SchedulerConfig, seed: int) -> tuple[_ProbeSample, float]:
-    torch.cuda.synchronize()
     t0 = time.perf_counter()
     if _probe_sample_kind() == "induced":
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
         s_crow, s_col, s_val, selected = _induced_sample_csr(crow, col, val, fraction=config.probe_fraction,
                                                              minimum_rows=config.probe_min_rows, seed=seed)
         return _ProbeSample(s_crow, s_col, s_val, selected, True, _threshold_translation(crow, s_crow, config)), t0
@@ -479,6 +567,15 @@ def _timed_sample(crow, col, val, config: SchedulerConfig, seed: int) -> tuple[_
     rows = crow.numel() - 1
     if fraction >= 0.999 or max(int(rows * fraction), config.probe_min_rows) >= rows:
         return _WholeGraph(crow, col, val), t0
+    if crow.is_cuda and load_native() and (val is None or val.dtype == torch.float32):
+        # the library cuts the rows out: no ATen sequence, no host synchronisation
+        k = min(max(int(rows * fraction), config.probe_min_rows, 1), rows)
+        gen = torch.Generator(device=crow.device)
+        gen.manual_seed(seed)
+        selected = torch.randperm(rows, generator=gen, device=crow.device)[:k].sort().values
+        capacity = min(nnz, int(1.25 * fraction * nnz) + (1 << 20))
+        s_crow, s_col, s_val, kept = _native.csr_row_sample(crow, col, val, selected, capacity)
+        return _DeviceRowSample(s_crow, s_col, s_val, selected, kept), t0
     s_crow, s_col, s_val, selected = _row_sample_csr(crow, col, val, fraction=fraction,
                                                      minimum_rows=config.probe_min_rows, seed=seed)
     return _ProbeSample(s_crow, s_col, s_val, selected, False, None), t0
@@ -521,10 +618,14 @@ def spmm_csr_auto(crow, col, val, x, *, guardrail: float = 0.95, k: int = 6, see
     sample, t0 = _timed_sample(crow, col, val, config, seed)
     s_crow, s_col, s_val = sample.crow, sample.col, sample.val
     s_x = sample.column_side(x)
-    torch.cuda.synchronize()
+    if sample.induced:
+        torch.cuda.synchronize()
     sample_ms = (time.perf_counter() - t0) * 1000.0
 
-    baseline, baseline_name = _prepare_spmm_baseline(s_crow, s_col, s_val, s_x)
+    def make_baseline():
+        e_crow, e_col, e_val = sample.exact()
+        return _prepare_spmm_baseline(e_crow, e_col, e_val, s_x)
+
     split = native_op("spmm_csr_split") if config.hub_split else None
     core = native_op("spmm_csr")
     runs: list[tuple[list[int], Callable[[], torch.Tensor]]] = []
@@ -537,8 +638,7 @@ def spmm_csr_auto(crow, col, val, x, *, guardrail: float = 0.95, k: int = 6, see
                          lambda t=tile, w=warps, h=sample.threshold(threshold): _probe_spmm(s_crow, s_col, s_val, s_x, t, w, h)))
     result = _probe_and_choose(
         operation="spmm", label="spmm", config=config, device=device, graph=graph, cache=cache,
-        sample_ms=sample_ms, probe_rows=sample.rows, probe_nonzeros=s_col.numel(),
-        baseline=baseline, baseline_name=baseline_name, candidates=runs,
+        sample_ms=sample_ms, sample=sample, make_baseline=make_baseline, candidates=runs,
         fallback=(lambda: _probe_spmm(s_crow, s_col, s_val, s_x, DEFAULT_TILE, DEFAULT_WARPS, DEFAULT_HUB_THRESHOLD))
         if core is not None else None, verbose=verbose,
         preferred=(DEFAULT_TILE, DEFAULT_WARPS, DEFAULT_HUB_THRESHOLD))
@@ -649,10 +749,14 @@ def sddmm_csr_auto(crow, col, query, key, *, guardrail: float = 0.95, seed: int 
     sample, t0 = _timed_sample(crow, col, None, config, seed)
     s_crow, s_col = sample.crow, sample.col
     s_query, s_key = sample.row_side(query), sample.column_side(key)
-    torch.cuda.synchronize()
+    if sample.induced:
+        torch.cuda.synchronize()
     sample_ms = (time.perf_counter() - t0) * 1000.0
 
-    baseline, baseline_name = _prepare_sddmm_baseline(s_crow, s_col, s_query, s_key)
+    def make_baseline():
+        e_crow, e_col, _ = sample.exact()
+        return _prepare_sddmm_baseline(e_crow, e_col, sample.exact_rows(s_query), s_key)
+
     split = native_op("sddmm_csr_split") if config.hub_split else None
     core = native_op("sddmm_csr")
     runs: list[tuple[list[int], Callable[[], torch.Tensor]]] = []
@@ -665,8 +769,7 @@ def sddmm_csr_auto(crow, col, query, key, *, guardrail: float = 0.95, seed: int 
                          lambda w=warps, h=sample.threshold(threshold): _probe_sddmm(s_crow, s_col, s_query, s_key, w, h)))
     result = _probe_and_choose(
         operation="sddmm", label="sddmm", config=config, device=device, graph=graph, cache=cache,
-        sample_ms=sample_ms, probe_rows=sample.rows, probe_nonzeros=s_col.numel(),
-        baseline=baseline, baseline_name=baseline_name, candidates=runs,
+        sample_ms=sample_ms, sample=sample, make_baseline=make_baseline, candidates=runs,
         fallback=(lambda: _probe_sddmm(s_crow, s_col, s_query, s_key, SDDMM_WARPS, SDDMM_HUB_THRESHOLD))
         if core is not None else None, verbose=verbose, preferred=(SDDMM_WARPS, SDDMM_HUB_THRESHOLD))
     output = _run_sddmm_choice(result["choice"], result["candidate"] if result["choice"] == "autosage" else None,
@@ -775,14 +878,21 @@ def csr_attention_forward(crow, col, query, key, value, *, guardrail: float = 0.
     sample, t0 = _timed_sample(crow, col, None, config, seed)
     s_crow, s_col = sample.crow, sample.col
     s_q, s_k, s_v = sample.row_side(query), sample.column_side(key), sample.column_side(value)
-    torch.cuda.synchronize()
+    if sample.induced:
+        torch.cuda.synchronize()
     sample_ms = (time.perf_counter() - t0) * 1000.0
 
-    def three_pass() -> torch.Tensor:
-        q = s_q if scale is None else s_q * scale
-        scores = _probe_sddmm(s_crow, s_col, q, s_k, SDDMM_WARPS, SDDMM_HUB_THRESHOLD)
-        return _probe_spmm(s_crow, s_col, _csr_row_softmax(s_crow, scores), s_v, DEFAULT_TILE, DEFAULT_WARPS,
-                           DEFAULT_HUB_THRESHOLD)
+    def make_baseline():
+        e_crow, e_col, _ = sample.exact()
+        e_q = sample.exact_rows(s_q)
+
+        def three_pass() -> torch.Tensor:
+            q = e_q if scale is None else e_q * scale
+            scores = _probe_sddmm(e_crow, e_col, q, s_k, SDDMM_WARPS, SDDMM_HUB_THRESHOLD)
+            return _probe_spmm(e_crow, e_col, _csr_row_softmax(e_crow, scores), s_v, DEFAULT_TILE, DEFAULT_WARPS,
+                               DEFAULT_HUB_THRESHOLD)
+
+        return three_pass, "sddmm+softmax+spmm"
 
     forced = config.warps_per_block is not None or config.hub_threshold is not None
     pairs = _with_library_default(_warp_threshold_pairs(crow, query.size(1), config), (8, 512), forced)
@@ -792,8 +902,7 @@ def csr_attention_forward(crow, col, query, key, value, *, guardrail: float = 0.
                      lambda w=warps, h=sample.threshold(threshold): _run_fused_attention(s_crow, s_col, s_q, s_k, s_v, scale, w, h)))
     result = _probe_and_choose(
         operation="attention", label="attention", config=config, device=device, graph=graph, cache=cache,
-        sample_ms=sample_ms, probe_rows=sample.rows, probe_nonzeros=s_col.numel(),
-        baseline=three_pass, baseline_name="sddmm+softmax+spmm", candidates=runs, fallback=None, verbose=verbose,
+        sample_ms=sample_ms, sample=sample, make_baseline=make_baseline, candidates=runs, fallback=None, verbose=verbose,
         preferred=(8, 512))
     return finish(result, False)
 

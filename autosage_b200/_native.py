@@ -50,6 +50,8 @@ SIGNATURES = {
     "asg_add_row_bias": (_INT, [_P, _P, _I64, _I64, _P]),
     "asg_csr_build_workspace_bytes": (_SZ, [_I64, _I64]),
     "asg_csr_from_edges": (_INT, [_P, _P, _P, _I64, _I64, _P, _P, _P, _P, _P, _SZ, _P]),
+    "asg_row_sample_workspace_bytes": (_SZ, [_I64]),
+    "asg_csr_row_sample": (_INT, [_P, _P, _P, _P, _I64, _I64, _P, _P, _P, _P, _P, _SZ, _P]),
     "asg_linear_bias": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "asg_linear_workspace_bytes": (_SZ, [_I64, _I64]),
     "asg_linear_supported": (_INT, [_I64, _I64]),
@@ -329,6 +331,27 @@ def csr_from_edges(row_of_edge: torch.Tensor, col_of_edge: torch.Tensor, values:
                                        None if permuted is None else permuted.data_ptr(), workspace.data_ptr(),
                                        workspace.numel(), _stream(device)))
     return crow, col, order, permuted
+
+
+def csr_row_sample(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor], rows: torch.Tensor,
+                   capacity: int):
+    """Cut the rows ``rows`` (ascending int64, on the device) out of a CSR, all their edges kept.
+    Returns (sample_crow[k + 1], sample_col[capacity], sample_val[capacity] or None, kept[2]) without
+    synchronising; ``kept`` = (rows kept, edges kept) is a device tensor."""
+    device = crow.device
+    k = rows.numel()
+    out_crow = torch.empty(k + 1, dtype=torch.long, device=device)
+    out_col = torch.empty(capacity, dtype=torch.long, device=device)
+    out_val = None if val is None else torch.empty(capacity, dtype=torch.float32, device=device)
+    kept = torch.empty(2, dtype=torch.long, device=device)
+    need = int(library().asg_row_sample_workspace_bytes(k))
+    if need == 0:
+        raise RuntimeError("asg_row_sample_workspace_bytes could not size the scan scratch")
+    workspace = torch.empty(need, dtype=torch.uint8, device=device)
+    check(library().asg_csr_row_sample(crow.data_ptr(), col.data_ptr(), _ptr(val), rows.data_ptr(), k, int(capacity),
+                                       out_crow.data_ptr(), out_col.data_ptr(), _ptr(out_val), kept.data_ptr(),
+                                       workspace.data_ptr(), workspace.numel(), _stream(device)))
+    return out_crow, out_col, out_val, kept
 
 
 def linear_bias(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:

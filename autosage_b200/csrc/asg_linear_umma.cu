@@ -11,9 +11,10 @@
 //   warp 1        lane 0 streams the weight pieces into a 3-stage shared-memory ring with 1-D bulk
 //                 async copies; the pieces were split once and stored in global memory in exactly the
 //                 128-byte-swizzled K-major image the MMA reads (asg::linear_umma::pack_weight)
-//   warps 4-7     epilogue: tensor memory -> registers (tcgen05.ld) -> + bias -> a per-warp staging
-//                 tile in shared memory -> coalesced streaming stores, 512 bytes per instruction
-//   warps 8-15    producers: read 128 rows x 64 features of x (float4 loads, 8 in flight per lane),
+//   warps 4-11    epilogue, two warps per tensor-memory lane quarter: tensor memory -> registers
+//                 (tcgen05.ld) -> + bias -> a per-warp staging tile in shared memory -> coalesced
+//                 streaming stores, 512 bytes per instruction
+//   warps 12-19   producers: read 128 rows x 64 features of x (float4 loads, 8 in flight per lane),
 //                 split them, write the three pieces into a 2-stage ring in the swizzled layout
 // The accumulator is double-buffered (2 x N tensor-memory columns), so the epilogue of tile t runs under
 // the MMAs of tile t+1, and the producers refill one 64-feature stage while the MMAs read the other.
@@ -21,7 +22,6 @@
 // CTA-wide abort flag and the CTA leaves through the common exit, which frees its tensor memory.
 #include "asg_umma.cuh"
 #include "asg_tile.cuh"
-#include <stdlib.h>
 
 namespace asg {
 namespace linear_umma {
@@ -76,7 +76,6 @@ struct Args {
   int rows, k, n;
   int k_blocks, n_tiles;
   unsigned tmem_columns;
-  int debug;
 };
 
 // One thread per weight element: split it and store the pieces where the MMA will read them.
@@ -208,7 +207,6 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const Args a) {
             alive = false;
             break;
           }
-          if ((a.debug & 4) && ib >= kBStages) { mbar_arrive(&bars->b_full[sb]); continue; }
           mbar_expect_tx(&bars->b_full[sb], stage_bytes);
           bulk_g2s(smem + Smem::b_ring + sb * kBStageStride, a.packed + static_cast<size_t>(s) * stage_bytes, stage_bytes,
                    &bars->b_full[sb]);
@@ -236,7 +234,6 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const Args a) {
       const long long row0 = static_cast<long long>(tile) * kBlockM + quarter * 32;
       const uint32_t acc = tmem_base + lane_base + buf * static_cast<uint32_t>(a.n);
       for (int chunk = parity; chunk < n_chunks; chunk += 2) {
-        if (a.debug & 32) break;
         float v[32];
         tmem_load_32x32(acc + chunk * 32, v);
         // row `lane` of the 32 x 32 block -> staging; the 16-byte chunk index is XORed with the row so
@@ -248,7 +245,6 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const Args a) {
               make_float4(v[j] + bj.x, v[j + 1] + bj.y, v[j + 2] + bj.z, v[j + 3] + bj.w);
         }
         __syncwarp();
-        if (a.debug & 8) continue;
         // staging -> global: each instruction stores four rows x 128 contiguous bytes
         float4 w[8];
 #pragma unroll
@@ -259,7 +255,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const Args a) {
         float* dst = a.out + (row0 + (lane >> 3)) * a.n + chunk * 32 + (lane & 7) * 4;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          if (row0 + i * 4 + (lane >> 3) < a.rows && !((a.debug & 1) && chunk > 0))
+          if (row0 + i * 4 + (lane >> 3) < a.rows)
             st_stream4(dst + static_cast<long long>(i) * 4 * a.n, w[i]);
         }
       }
@@ -282,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const Args a) {
         for (int i = 0; i < 8; ++i) {
           const int r = pw * 16 + i * 2 + half;
           const long long g = static_cast<long long>(tile) * kBlockM + r;
-          if (g < a.rows && !((a.debug & 2) && tile != first_tile)) {
+          if (g < a.rows) {
             VecIO<4>::load(v[i], a.x + g * a.k + kb * kBlockK + c * 4, pol_stream);
           } else {
             v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f;
@@ -299,7 +295,6 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const Args a) {
         unsigned char* stage = smem + Smem::a_ring + sa * kAStageBytes;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          if ((a.debug & 16) && tile != first_tile) break;
           const int r = pw * 16 + i * 2 + half;
           const Pieces2 p0 = split_pair(v[i][0], v[i][1]);
           const Pieces2 p1 = split_pair(v[i][2], v[i][3]);
@@ -386,7 +381,6 @@ extern "C" int asg_linear_bias_umma(const float* x, const float* weight, const f
   unsigned columns = 32;
   while (columns < 2u * static_cast<unsigned>(n)) columns <<= 1;  // two accumulators, a power of two >= 32
   args.tmem_columns = columns;
-  args.debug = getenv("ASG_LINEAR_DEBUG") ? atoi(getenv("ASG_LINEAR_DEBUG")) : 0;
   ASG_CUDA(cudaFuncSetAttribute(linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamicSmem));
   const int sms = sm_count(guard.target);
   const int grid = args.n_tiles < sms ? args.n_tiles : sms;

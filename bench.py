@@ -414,6 +414,42 @@ def run_ours_single(args) -> dict:
                                   "value": round(algorithmic / (cusparse_ms * 1e-3) / 1e9, 2), "unit": "GB/s"}
         del matrix, weights
 
+    if not args.no_cpu_baseline and args.workload in ("c3_sddmm", "c4_attention"):
+        # The reference's CPU path for these operators (gather-dot SDDMM; SDDMM -> row softmax ->
+        # torch.sparse.mm for attention) on the first rows holding ~1 M edges: the gather-dot
+        # materialises two [edges, F] operands, so the sample is kept small.
+        from oracle import oracle
+
+        torch.set_num_threads(max(1, os.cpu_count() or 1))
+        crow_c = crow.cpu()
+        target = min(1_000_000, nnz)
+        rows = int(torch.searchsorted(crow_c, torch.tensor(target)).clamp(1, n))
+        sub_crow = crow_c[: rows + 1].contiguous()
+        sample_nnz = int(sub_crow[-1])
+        sub_col = col[:sample_nnz].cpu()
+        q_c, k_c = w["q"][:rows].cpu(), w["k"].cpu()
+        if args.workload == "c3_sddmm":
+            run_cpu = lambda: oracle.sddmm_reference_cpu(sub_crow, sub_col, q_c, k_c)  # noqa: E731
+            sample_bytes, what = sddmm_bytes(rows, sample_nnz, f), "gather-dot SDDMM on CPU float32"
+        else:
+            v_c = w["v"].cpu()
+            run_cpu = lambda: oracle.attention_reference_cpu(sub_crow, sub_col, q_c, k_c, v_c, f ** -0.5)  # noqa: E731
+            sample_bytes, what = attention_bytes(rows, sample_nnz, f), "SDDMM -> row softmax -> torch.sparse.mm on CPU float32"
+        laps = []
+        for _ in range(3):
+            t0 = time.perf_counter()
+            run_cpu()
+            laps.append(time.perf_counter() - t0)
+        seconds = min(laps[1:])
+        line["cpu_baseline"] = {
+            "value": round(sample_bytes / seconds / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(),
+            "host_cpus": os.cpu_count(), "kind": "port",
+            "sample": f"first {rows} rows ({sample_nnz} nnz) of the same CSR against the full K"
+                      + (" and V" if args.workload == "c4_attention" else "") + f"; {what} (the reference's CPU path), "
+                      f"best of 2 after 1 warm-up, {seconds:.3f} s per call",
+            "edges_f_per_s": round(sample_nnz * f / seconds, 1),
+        }
+
     if not args.no_cpu_baseline and args.workload in ("c2_spmm", "c5_spmm"):
         from oracle import oracle
 
@@ -435,6 +471,45 @@ def run_ours_single(args) -> dict:
             "oracle_threads": oracle.threads(),
         }
     return line
+
+
+def small_cpu_case() -> dict:
+    """The reference's CPU-runnable configuration: unweighted spmm_csr on a 4096-row CSR (degree uniform in
+    [1, 32], distinct columns), X 4096 x 64, through the package's CPU path (torch.sparse.mm over a CSR
+    tensor, rebuilt per call as in autosage/ops.py:124-143): 3 warm-ups, 20 timed calls, min and median;
+    and the same call on the GPU, which at this size is launch-bound."""
+    import autosage_b200
+    from benchlib import synthetic as syn
+
+    crow, col = syn.uniform_degree_csr(4096, 32, seed=0)
+    x = syn.dense(4096, 64, 3)
+    threads_before = torch.get_num_threads()
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
+    laps = []
+    for i in range(23):
+        t0 = time.perf_counter()
+        y_cpu = autosage_b200.spmm_csr(crow, col, None, x)
+        if i >= 3:
+            laps.append((time.perf_counter() - t0) * 1e3)
+    found = {"workload": f"c1: spmm_csr unweighted, 4096 rows, {col.numel()} nnz, F=64, CPU tensors",
+             "cpu_ms_min": round(min(laps), 4), "cpu_ms_median": round(statistics.median(laps), 4),
+             "cores": torch.get_num_threads(), "calls": 20}
+    torch.set_num_threads(threads_before)
+    if torch.cuda.is_available():
+        dev = torch.device("cuda", 0)
+        crow_d, col_d, x_d = crow.to(dev), col.to(dev), x.to(dev)
+        for _ in range(3):
+            y_gpu = autosage_b200.spmm_csr(crow_d, col_d, None, x_d)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(20):
+            y_gpu = autosage_b200.spmm_csr(crow_d, col_d, None, x_d)
+        end.record()
+        torch.cuda.synchronize()
+        found["gpu_ms_per_call"] = round(begin.elapsed_time(end) / 20, 4)
+        found["gpu_matches_cpu"] = bool(torch.allclose(y_gpu.cpu(), y_cpu, rtol=1e-4, atol=1e-4))
+    return found
 
 
 def conv_workload_label(n: int, nnz: int, f: int, out_f: int = 256) -> str:

@@ -105,15 +105,20 @@ def _single_gpu_extras(args, bench, shard, layer, algorithmic, n, nnz, f, out_f,
                                       host_cpus=os.cpu_count(), edges_f_per_s=ref["edges_f_per_s"])
     if not getattr(args, "no_other_configs", False):
         others = {}
-        for workload, tile in (("c2_spmm", 64), ("c3_sddmm", 64), ("c4_attention", 64)):
+        cases = (("c2_spmm", "c2_spmm", 64, 128), ("c3_sddmm", "c3_sddmm", 64, 128), ("c4_attention", "c4_attention", 64, 128),
+                 ("c2_spmm_f64", "c2_spmm", 64, 64), ("c2_spmm_f256", "c2_spmm", 64, 256), ("c3_sddmm_f64", "c3_sddmm", 64, 64),
+                 ("c5_spmm_f256", "c5_spmm", 128, 256))
+        for label, workload, tile, features in cases:
             sub = argparse.Namespace(**vars(args))
-            sub.workload, sub.tile, sub.no_cpu_baseline = workload, tile, True
+            sub.workload, sub.tile, sub.features = workload, tile, features
+            # the CPU baselines of SDDMM and attention are timed once, on the F = 128 runs
+            sub.no_cpu_baseline = args.no_cpu_baseline or not (label in ("c3_sddmm", "c4_attention"))
             sub.steps, sub.warmup = min(args.steps, 10), 3
             sub.warps, sub.hub_threshold = {"c3_sddmm": (8, 8192), "c4_attention": (8, 512)}.get(workload, (4, 1024))
             torch.cuda.empty_cache()
             try:
                 got = bench.run_ours_single(sub)
-                others[workload] = {"workload": got["config"]["workload"], "ms_per_step": got["ms_per_step"],
+                others[label] = {"workload": got["config"]["workload"], "ms_per_step": got["ms_per_step"],
                                     "value": got["value"], "unit": got["unit"],
                                     "edges_f_per_s": got["edges_f_per_s"],
                                     "roofline_frac": got["roofline"]["frac"],
@@ -121,10 +126,69 @@ def _single_gpu_extras(args, bench, shard, layer, algorithmic, n, nnz, f, out_f,
                                     "e2e_value": got["e2e"]["value"],
                                     "e2e_graph_resident_value": got["e2e_graph_resident"]["value"],
                                     "gpu_launches": got["gpu_launches"]}
+                if "cpu_baseline" in got:
+                    others[label]["cpu_baseline"] = got["cpu_baseline"]
+                if "gpu_comparator" in got:
+                    others[label]["gpu_comparator_cusparse_ms"] = got["gpu_comparator"]["ms_per_step"]
             except Exception as exc:  # noqa: BLE001 - the headline line must still be printed
-                others[workload] = {"error": f"{type(exc).__name__}: {exc}"}
+                others[label] = {"error": f"{type(exc).__name__}: {exc}"}
         extras["other_configs"] = others
+        try:
+            extras["c1_cpu_case"] = bench.small_cpu_case()
+        except Exception as exc:  # noqa: BLE001
+            extras["c1_cpu_case"] = {"error": f"{type(exc).__name__}: {exc}"}
+        # the reference's own CUDA kernels, rebuilt for sm_100a, in a process of their own
+        from benchlib import reference_kernels
+
+        torch.cuda.empty_cache()
+        extras["gpu_comparator_reference"] = {
+            label: reference_kernels.run_in_subprocess(workload, 128)
+            for label, workload in (("c2_spmm", "c2_spmm"), ("c3_sddmm", "c3_sddmm"), ("c5_spmm", "c5_spmm"))}
+        extras["probe_ms_uncached"] = _probe_costs(bench, args, device)
     return extras
+
+
+def _probe_costs(bench, args, device) -> dict:
+    """Wall time of one scheduled call with an empty schedule cache (sample + probe + guardrail + the
+    full-graph run it ends with) and of the same call replayed from the cache, per configuration."""
+    import tempfile
+
+    import autosage_b200
+
+    found = {}
+    saved = os.environ.get("AUTOSAGE_CACHE_DIR")
+    for name, workload in (("c2", "c2_spmm"), ("c4", "c4_attention"), ("c5", "c5_spmm")):
+        torch.cuda.empty_cache()
+        try:
+            w = bench.build_workload(workload, args.features, device)
+            os.environ["AUTOSAGE_CACHE_DIR"] = tempfile.mkdtemp(prefix="autosage-bench-cache-")
+            if workload == "c4_attention":
+                def call():
+                    return autosage_b200.csr_attention_forward(w["crow"], w["col"], w["q"], w["k"], w["v"],
+                                                               scale=args.features ** -0.5)[1]["attention"]
+            else:
+                def call():
+                    return autosage_b200.spmm_csr_auto(w["crow"], w["col"], w["val"], w["x"])[1]
+            laps = []
+            for _ in range(2):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                info = call()
+                torch.cuda.synchronize()
+                laps.append((time.perf_counter() - t0) * 1e3)
+                if not laps[1:]:
+                    first = info
+            found[name] = {"uncached_ms": round(laps[0], 2), "replay_ms": round(laps[1], 3), "choice": first["choice"],
+                           "candidate": first["candidate"], "probe_rows": first.get("probe_rows"),
+                           "probe_nonzeros": first.get("probe_nonzeros"), "replayed_from_cache": bool(info["from_cache"])}
+            del w
+        except Exception as exc:  # noqa: BLE001 - the headline line must still be printed
+            found[name] = {"error": f"{type(exc).__name__}: {exc}"}
+    if saved is None:
+        os.environ.pop("AUTOSAGE_CACHE_DIR", None)
+    else:
+        os.environ["AUTOSAGE_CACHE_DIR"] = saved
+    return found
 
 
 def run(args):

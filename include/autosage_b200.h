@@ -177,6 +177,25 @@ int asg_csr_from_edges(const int64_t* row_of_edge, const int64_t* col_of_edge, c
                        float* val_out, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Row sample for the scheduler's probe: the rows listed in rows[n_sampled_rows] (device, int64,
+ * ascending) are cut out of the CSR with every one of their edges and their column ids unchanged:
+ *   out_crow[n_sampled_rows + 1]  row pointers of the sample
+ *   out_col / out_val[capacity]   the rows' column and weight segments, one after the other
+ *   kept[2]                       {rows kept, edges kept}: if the sampled rows hold more than `capacity`
+ *                                 edges, only the leading rows that fit are copied and the remaining row
+ *                                 pointers repeat the last value (empty rows), so the arrays are always a
+ *                                 valid CSR of n_sampled_rows rows
+ * Three small kernels and one device-wide scan, no host synchronisation; the caller reads kept[] when it
+ * next synchronises.  Replaces the ATen sequence (and its .item() synchronisation) with which the
+ * reference builds its probe sample, autosage/_auto.py:95-154.  The workspace holds
+ * asg_row_sample_workspace_bytes(n_sampled_rows) bytes, 256-byte aligned.
+ */
+size_t asg_row_sample_workspace_bytes(int64_t n_sampled_rows);
+int asg_csr_row_sample(const int64_t* crow, const int64_t* col, const float* val, const int64_t* rows,
+                       int64_t n_sampled_rows, int64_t capacity, int64_t* out_crow, int64_t* out_col,
+                       float* out_val, int64_t* kept, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * out[rows, out_features] = x[rows, in_features] @ weight[out_features, in_features]^T + bias:
  * the layer's nn.Linear (autosage/conv.py:55) at float32 accuracy on the tensor cores (each float32
  * operand is split into three bfloat16 pieces, the piece products are summed in float32; no TF32

@@ -189,3 +189,45 @@ def spmm_reference_cpu(crow, col, val, x):
     weights = torch.ones(col.numel(), dtype=x.dtype) if val is None else val.to(x.dtype)
     matrix = torch.sparse_csr_tensor(crow, col, weights, size=(crow.numel() - 1, x.size(0)), dtype=x.dtype)
     return torch.sparse.mm(matrix, x)
+
+
+def sddmm_reference_cpu(crow, col, query, key):
+    """The reference's CPU SDDMM exactly as it runs it (the gather-dot baseline its scheduler falls
+    back to on CPU tensors, autosage/_auto.py:79-92): expand the row id of every edge, gather both
+    operands, multiply and sum over the feature axis.  torch CPU tensors in and out; ``query`` holds one
+    row per CSR row, ``key`` is indexed by column id.  Used as a timed CPU baseline."""
+    import torch
+
+    counts = (crow[1:] - crow[:-1]).to(torch.long)
+    rows = torch.repeat_interleave(torch.arange(crow.numel() - 1, dtype=torch.long), counts)
+    return (query.index_select(0, rows) * key.index_select(0, col)).sum(dim=1)
+
+
+def row_softmax_reference_cpu(crow, scores):
+    """The reference's CSR row softmax (autosage/_auto.py:744-759): scatter amax, exp of the shifted
+    scores, scatter add, divide."""
+    import torch
+
+    row_count = crow.numel() - 1
+    counts = (crow[1:] - crow[:-1]).to(torch.long)
+    rows = torch.repeat_interleave(torch.arange(row_count, dtype=torch.long), counts)
+    if scores.numel() == 0:
+        return scores.clone()
+    maxima = torch.full((row_count,), -torch.inf, dtype=scores.dtype)
+    maxima.scatter_reduce_(0, rows, scores, reduce="amax", include_self=True)
+    exponentials = (scores - maxima.index_select(0, rows)).exp()
+    denominators = torch.zeros_like(maxima).scatter_add_(0, rows, exponentials)
+    return exponentials / denominators.index_select(0, rows)
+
+
+def attention_reference_cpu(crow, col, query, key, value, scale: float = 1.0):
+    """The reference's attention pipeline on CPU tensors (autosage/_auto.py:762-780 with every stage on
+    its CPU path): gather-dot SDDMM of the (scaled) queries, CSR row softmax, torch.sparse.mm with the
+    probabilities as edge weights.  ``query`` holds one row per CSR row; ``key``/``value`` are indexed
+    by column id."""
+    import torch
+
+    scores = sddmm_reference_cpu(crow, col, query * scale if scale != 1.0 else query, key)
+    weights = row_softmax_reference_cpu(crow, scores)
+    matrix = torch.sparse_csr_tensor(crow, col, weights, size=(crow.numel() - 1, value.size(0)), dtype=value.dtype)
+    return torch.sparse.mm(matrix, value)

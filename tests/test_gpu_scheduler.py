@@ -355,3 +355,52 @@ def test_probe_on_row_sample_prefers_the_kernels(asg, isolated_cache, monkeypatc
     monkeypatch.setenv("AUTOSAGE_CACHE", "0")
     _, sched = asg.sddmm_csr_auto(crow, col, q, k)
     assert sched["probe_nonzeros"] < 0.01 * info["nnz"]
+
+
+def test_native_row_sample_is_bit_exact(asg):
+    """asg_csr_row_sample against the torch formulation of the same sample (integer outputs bit-exact,
+    weights copied verbatim), and its behaviour when the selected rows exceed the capacity."""
+    from autosage_b200 import _auto, _native
+
+    dev = torch.device("cuda")
+    crow, col = random_csr(6000, 9, seed=77, hubs={5: 4000, 4100: 1500})
+    val = weights(col.numel(), 3)
+    crow_d, col_d, val_d = crow.to(dev), col.to(dev), val.to(dev)
+    ref_crow, ref_col, ref_val, selected = _auto._row_sample_csr(crow_d, col_d, val_d, fraction=0.3, minimum_rows=8, seed=4)
+    total = ref_col.numel()
+    for weights_given in (True, False):
+        s_crow, s_col, s_val, kept = _native.csr_row_sample(crow_d, col_d, val_d if weights_given else None, selected,
+                                                            total + 100)
+        assert kept.tolist() == [selected.numel(), total]
+        assert torch.equal(s_crow, ref_crow) and torch.equal(s_col[:total], ref_col)
+        assert (s_val is None) == (not weights_given)
+        if weights_given:
+            assert torch.equal(s_val[:total], ref_val)
+    # capacity below the total: only the leading rows that fit are copied, the tail rows are empty
+    capacity = int(ref_crow[selected.numel() // 2])
+    s_crow, s_col, _, kept = _native.csr_row_sample(crow_d, col_d, None, selected, capacity)
+    rows_kept, edges_kept = kept.tolist()
+    assert edges_kept <= capacity and edges_kept == int(ref_crow[rows_kept])
+    assert rows_kept == selected.numel() or int(ref_crow[rows_kept + 1]) > capacity
+    assert torch.equal(s_crow[: rows_kept + 1], ref_crow[: rows_kept + 1])
+    assert bool((s_crow[rows_kept:] == edges_kept).all())
+    assert torch.equal(s_col[:edges_kept], ref_col[:edges_kept])
+    # nothing selected
+    empty = _native.csr_row_sample(crow_d, col_d, None, selected[:0], 16)
+    assert empty[0].tolist() == [0] and empty[3].tolist() == [0, 0]
+
+
+def test_scheduler_probe_uses_the_device_sample(asg, isolated_cache, monkeypatch):
+    """Above the probe's edge target the sample is cut by the library; the schedule reports the
+    sample's real sizes and the replayed call gives the same result as the plain operator."""
+    from benchlib import synthetic as syn
+
+    dev = torch.device("cuda")
+    crow, col, info = syn.powerlaw_csr(syn.ARXIV_LIKE, seed=0, device=dev)
+    n = info["rows"]
+    x = syn.dense(n, 64, 3, dev)
+    monkeypatch.setenv("AUTOSAGE_PROBE_EDGES", "600000")
+    y, schedule = asg.spmm_csr_auto(crow, col, None, x)
+    assert 0 < schedule["probe_rows"] < n and 0.1 * info["nnz"] < schedule["probe_nonzeros"] < 0.5 * info["nnz"]
+    assert len(schedule["candidates"]) >= 2 and all(c["iterations"] >= 1 for c in schedule["candidates"])
+    assert torch.allclose(y, torch.ops.autosage.spmm_csr(crow, col, None, x), rtol=1e-4, atol=1e-3)
