@@ -819,7 +819,7 @@ def _run_fused_attention(crow, col, query, key, value, scale, warps, threshold) 
     out = torch.empty_like(query)  # one output row per CSR row (the probe's row sample is k x N)
     if out.numel() == 0:
         return out
-    workspace, ready = _native.planned_workspace(crow, threshold)
+    workspace, ready = _native.planned_workspace(crow, threshold, _native.attention_extra_bytes(crow.numel() - 1))
     _native.attention(crow, col, query, key, value, out, scale=1.0 if scale is None else float(scale),
                       warps=warps, threshold=threshold, flags=_base_flags() | ready, workspace=workspace)
     return out

@@ -46,6 +46,7 @@ SIGNATURES = {
     "asg_sddmm_csr_split": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _I64, _P, _SZ, _P]),
     "asg_sddmm_csr_ex": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_csr_row_softmax": (_INT, [_P, _P, _P, _I64, _I64, _INT, _I64, _U32, _P, _SZ, _P]),
+    "asg_attention_workspace_bytes": (_SZ, [_I64]),
     "asg_csr_attention": (_INT, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _F32, _INT, _I64, _U32, _P, _SZ, _P]),
     "asg_add_row_bias": (_INT, [_P, _P, _I64, _I64, _P]),
     "asg_csr_build_workspace_bytes": (_SZ, [_I64, _I64]),
@@ -57,6 +58,7 @@ SIGNATURES = {
     "asg_linear_supported": (_INT, [_I64, _I64]),
     "asg_linear_bias_umma": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
     "asg_copy_2d": (_INT, [_P, _SZ, _P, _SZ, _SZ, _SZ, _P]),
+    "asg_push_to_peers": (_INT, [_P, _P, _INT, _SZ, _INT, _P]),
     "asg_workspace_status": (_INT, [_P, _P, _P]),
     "asg_spmm_csr_split_noalloc": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _P]),
     "asg_static_max_rows": (_I64, []),
@@ -143,8 +145,8 @@ def _capturing() -> bool:
     return torch.cuda.is_current_stream_capturing()
 
 
-def scratch(device: torch.device, n_rows: int) -> torch.Tensor:
-    need = workspace_bytes(n_rows)
+def scratch(device: torch.device, n_rows: int, extra_bytes: int = 0) -> torch.Tensor:
+    need = workspace_bytes(n_rows) + int(extra_bytes)
     if _capturing():
         # a captured launch keeps the raw pointer: the buffer has to come from the graph's own pool
         # (and so live as long as the graph), not from a cache that may replace it later
@@ -157,7 +159,12 @@ def scratch(device: torch.device, n_rows: int) -> torch.Tensor:
     return buffer
 
 
-def planned_workspace(crow: torch.Tensor, threshold: int) -> tuple[torch.Tensor, int]:
+def attention_extra_bytes(n_rows: int) -> int:
+    """Bytes beyond ``workspace_bytes`` that let the fused attention kernel split very long rows."""
+    return int(library().asg_attention_workspace_bytes(int(n_rows))) - workspace_bytes(n_rows)
+
+
+def planned_workspace(crow: torch.Tensor, threshold: int, extra_bytes: int = 0) -> tuple[torch.Tensor, int]:
     """Workspace holding the degree-binned plan of ``crow`` for ``threshold``.
 
     Returns ``(buffer, flags)`` where flags is ``FLAG_PLAN_READY`` when the buffer already holds
@@ -170,8 +177,8 @@ def planned_workspace(crow: torch.Tensor, threshold: int) -> tuple[torch.Tensor,
     memory pool, and the plan is rebuilt by the captured launches themselves.
     """
     if _capturing() or os.getenv("AUTOSAGE_PLAN_CACHE", "1") in ("0", "false", "off", "no"):
-        return scratch(crow.device, crow.numel() - 1), 0
-    key = (crow.data_ptr(), crow.numel(), int(threshold), crow.device.index, _stream(crow.device))
+        return scratch(crow.device, crow.numel() - 1, extra_bytes), 0
+    key = (crow.data_ptr(), crow.numel(), int(threshold), crow.device.index, _stream(crow.device), int(extra_bytes))
     entry = _PLANS.get(key)
     if entry is not None:
         ref, version, buffer, built = entry
@@ -179,7 +186,8 @@ def planned_workspace(crow: torch.Tensor, threshold: int) -> tuple[torch.Tensor,
             _PLANS.move_to_end(key)
             return buffer, (FLAG_PLAN_READY if built else 0)
         _forget(key)
-    buffer = torch.empty(max(workspace_bytes(crow.numel() - 1), 256), dtype=torch.uint8, device=crow.device)
+    buffer = torch.empty(max(workspace_bytes(crow.numel() - 1), 256) + int(extra_bytes), dtype=torch.uint8,
+                         device=crow.device)
     entry = [weakref.ref(crow), crow._version, buffer, False]
     _PLANS[key] = entry
     _UNBUILT[buffer.data_ptr()] = entry
@@ -375,6 +383,16 @@ def linear_bias_umma(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch
                                          out.data_ptr(), x.size(0), x.size(1), weight.size(0), workspace.data_ptr(),
                                          workspace.numel(), _stream(x.device)))
     return workspace
+
+
+def push_to_peers(src: torch.Tensor, destinations: list[torch.Tensor], n_ctas: int = 32) -> None:
+    """Store the contiguous tensor ``src`` into every tensor of ``destinations`` (same shape; peer-mapped
+    memory of other GPUs) from ``n_ctas`` CTAs on the current stream."""
+    if not destinations or src.numel() == 0:
+        return
+    pointers = (ctypes.c_void_p * len(destinations))(*[d.data_ptr() for d in destinations])
+    check(library().asg_push_to_peers(src.data_ptr(), pointers, len(destinations), src.numel() * src.element_size(),
+                                      int(n_ctas), _stream(src.device)))
 
 
 def workspace_status(workspace: torch.Tensor) -> int:

@@ -103,6 +103,30 @@ __global__ void __launch_bounds__(512) csr_softmax_kernel(const SoftmaxArgs a) {
 }
 
 // ------------------------------------------------------------------------------ fused attention
+// Rows of kSplitDegree edges or more ("mega rows") are not walked by one CTA: they are cut into
+// segments of kSegmentEdges edges, every segment is a work item of its own, each CTA leaves its
+// segment's (running maximum, running sum, un-normalised accumulator) in the split area, and the CTA
+// that finishes a row's last segment merges them (the same merge the warps of one CTA do).  Without
+// this the longest row of a power-law graph (13,000 edges on the 169,343-row benchmark graph) keeps one
+// CTA busy for most of the launch.  The area lives behind the plan in the workspace and is optional.
+constexpr int kSplitDegree = 4096;    // a power of two: such rows are exactly the front of the hub order
+constexpr int kSegmentEdges = 1024;
+constexpr int kMaxSegments = 512;
+constexpr int kMaxSplitRows = 128;
+constexpr int kPartialStride = 2 + 512;  // m, l, accumulator of up to 512 features
+
+struct SplitArea {
+  int n_split;     // hub rows order[0 .. n_split) are processed in segments
+  int n_segments;
+  int pad[2];
+  int first_segment[kMaxSplitRows];
+  int segment_count[kMaxSplitRows];
+  int done[kMaxSplitRows];
+  int segment_hub[kMaxSegments];    // index into the hub order
+  int segment_index[kMaxSegments];  // which segment of that row
+  float partial[kMaxSegments][kPartialStride];
+};
+
 struct AttentionArgs {
   const int64_t* crow;
   const int64_t* col;
@@ -112,9 +136,36 @@ struct AttentionArgs {
   float* out;
   Header* header;
   const int* order;
+  SplitArea* split;  // null: no row is split
   int f;
   float scale;
 };
+
+// One thread lists the segments of the mega rows (they lead the hub order: hubs are sorted by
+// descending floor(log2 degree)) and clears the per-row completion counters.
+__global__ void attention_split_plan(const AttentionArgs a) {
+  SplitArea* area = a.split;
+  const int n_hub = a.header->n_hub;
+  int rows = 0, segments = 0;
+  while (rows < n_hub && rows < kMaxSplitRows) {
+    const int row = a.order[rows];
+    const long long degree = a.crow[row + 1] - a.crow[row];
+    if (degree < kSplitDegree) break;
+    const int count = static_cast<int>((degree + kSegmentEdges - 1) / kSegmentEdges);
+    if (segments + count > kMaxSegments) break;
+    area->first_segment[rows] = segments;
+    area->segment_count[rows] = count;
+    area->done[rows] = 0;
+    for (int s = 0; s < count; ++s) {
+      area->segment_hub[segments] = rows;
+      area->segment_index[segments] = s;
+      ++segments;
+    }
+    ++rows;
+  }
+  area->n_split = rows;
+  area->n_segments = segments;
+}
 
 // Loads the row of Q a warp works on into registers (lane l of a group owns floats VW*(l+G*v)+i).
 template <int VW, int G, int NV>
@@ -202,18 +253,19 @@ __device__ __forceinline__ void attention_one_batch(const AttentionArgs& a, int 
 
 // All batches of one row that this warp is responsible for (first, first+stride, ...).
 template <int VW, int G, int NV, int U>
-__device__ __forceinline__ void attention_batches(const AttentionArgs& a, int row, long long first, long long stride,
-                                                  int lane, uint64_t pol_keep, uint64_t pol_stream, float& m_run,
-                                                  float& l_run, float (&acc)[NV][VW]) {
-  const long long e = a.crow[row + 1];
+__device__ __forceinline__ void attention_batches(const AttentionArgs& a, int row, long long first, long long e,
+                                                  long long stride, int lane, uint64_t pol_keep, uint64_t pol_stream,
+                                                  float& m_run, float& l_run, float (&acc)[NV][VW]) {
   float q[NV][VW];
   bool fvalid[NV];
   int foff[NV];
   attention_load_q<VW, G, NV>(a, row, lane, pol_stream, q, fvalid, foff);
+  int c_next = 0;  // the next batch's columns are fetched while the current batch gathers
+  if (first + lane < e) c_next = static_cast<int>(ld_index(a.col + first + lane, pol_stream));
   for (long long p = first; p < e; p += stride) {
     const int cnt = e - p < 32 ? static_cast<int>(e - p) : 32;
-    int c_l = 0;
-    if (lane < cnt) c_l = static_cast<int>(ld_index(a.col + p + lane, pol_stream));
+    const int c_l = c_next;
+    if (p + stride + lane < e) c_next = static_cast<int>(ld_index(a.col + p + stride + lane, pol_stream));
     attention_one_batch<VW, G, NV, U>(a, c_l, cnt, lane, q, fvalid, foff, pol_keep, m_run, l_run, acc);
   }
 }
@@ -240,23 +292,33 @@ __global__ void __launch_bounds__(512) attention_kernel(const AttentionArgs a) {
   const int f = a.f;
 
   if (n_hub > 0) {
+    const int n_split = a.split != nullptr ? a.split->n_split : 0;
+    const int n_segments = a.split != nullptr ? a.split->n_segments : 0;
+    const int n_items = n_segments + (n_hub - n_split);  // segments of the mega rows first, then whole hub rows
     for (;;) {
       __syncthreads();
       if (tid == 0) {
         const unsigned long long it = atomicAdd(&a.header->counter[0], 1ull);
-        *s_item = it < static_cast<unsigned long long>(n_hub) ? static_cast<int>(it) : -1;
+        *s_item = it < static_cast<unsigned long long>(n_items) ? static_cast<int>(it) : -1;
       }
       __syncthreads();
       const int item = *s_item;
       if (item < 0) break;
-      const int row = a.order[item];
+      const bool segment = item < n_segments;
+      const int hub = segment ? a.split->segment_hub[item] : n_split + (item - n_segments);
+      const int row = a.order[hub];
+      long long begin = a.crow[row], end = a.crow[row + 1];
+      if (segment) {
+        begin += static_cast<long long>(a.split->segment_index[item]) * kSegmentEdges;
+        if (begin + kSegmentEdges < end) end = begin + kSegmentEdges;
+      }
       float m_run = -CUDART_INF_F, l_run = 0.f;
       float acc[NV][VW];
 #pragma unroll
       for (int v = 0; v < NV; ++v)
 #pragma unroll
         for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
-      attention_batches<VW, G, NV, U>(a, row, a.crow[row] + 32ll * warp, 32ll * n_warps, lane, pol_keep, pol_stream,
+      attention_batches<VW, G, NV, U>(a, row, begin + 32ll * warp, end, 32ll * n_warps, lane, pol_keep, pol_stream,
                                       m_run, l_run, acc);
 #pragma unroll
       for (int o = G; o < 32; o <<= 1)
@@ -279,6 +341,7 @@ __global__ void __launch_bounds__(512) attention_kernel(const AttentionArgs a) {
       for (int w = 1; w < n_warps; ++w) m_all = fmaxf(m_all, s_m[w]);
       float l_all = 0.f;
       for (int w = 0; w < n_warps; ++w) l_all += s_l[w] * expf(s_m[w] - m_all);  // idle warps: 0 * exp(-inf) = 0
+      float* partial = segment ? a.split->partial[item] : nullptr;
       for (int i = tid; i < FT; i += blockDim.x) {
         if (i < f) {
           float t = 0.f;
@@ -286,7 +349,40 @@ __global__ void __launch_bounds__(512) attention_kernel(const AttentionArgs a) {
             const float weight = s_l[w] > 0.f ? expf(s_m[w] - m_all) : 0.f;
             t = fmaf(s_acc[w * FT + i], weight, t);
           }
-          st_stream1(a.out + static_cast<size_t>(row) * f + i, l_all > 0.f ? t / l_all : 0.f);
+          if (segment) partial[2 + i] = t;  // un-normalised: the row's merge divides
+          else st_stream1(a.out + static_cast<size_t>(row) * f + i, l_all > 0.f ? t / l_all : 0.f);
+        }
+      }
+      if (segment) {
+        if (tid == 0) {
+          partial[0] = m_all;
+          partial[1] = l_all;
+        }
+        // the CTA that completes the row's last segment merges all of them
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) *s_item = atomicAdd(&a.split->done[hub], 1) == a.split->segment_count[hub] - 1 ? 1 : 0;
+        __syncthreads();
+        if (*s_item == 1) {
+          __threadfence();
+          const int first = a.split->first_segment[hub];
+          const int count = a.split->segment_count[hub];
+          float m_row = -CUDART_INF_F;
+          for (int k = 0; k < count; ++k) m_row = fmaxf(m_row, __ldcg(&a.split->partial[first + k][0]));
+          float l_row = 0.f;
+          for (int k = 0; k < count; ++k) {
+            const float l_k = __ldcg(&a.split->partial[first + k][1]);
+            if (l_k > 0.f) l_row += l_k * expf(__ldcg(&a.split->partial[first + k][0]) - m_row);
+          }
+          for (int i = tid; i < f; i += blockDim.x) {
+            float t = 0.f;
+            for (int k = 0; k < count; ++k) {
+              const float l_k = __ldcg(&a.split->partial[first + k][1]);
+              const float weight = l_k > 0.f ? expf(__ldcg(&a.split->partial[first + k][0]) - m_row) : 0.f;
+              t = fmaf(__ldcg(&a.split->partial[first + k][2 + i]), weight, t);
+            }
+            st_stream1(a.out + static_cast<size_t>(row) * f + i, l_row > 0.f ? t / l_row : 0.f);
+          }
         }
       }
     }
@@ -305,7 +401,8 @@ __global__ void __launch_bounds__(512) attention_kernel(const AttentionArgs a) {
       for (int v = 0; v < NV; ++v)
 #pragma unroll
         for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
-      attention_batches<VW, G, NV, U>(a, row, a.crow[row], 32ll, lane, pol_keep, pol_stream, m_run, l_run, acc);
+      attention_batches<VW, G, NV, U>(a, row, a.crow[row], a.crow[row + 1], 32ll, lane, pol_keep, pol_stream, m_run,
+                                      l_run, acc);
 #pragma unroll
       for (int o = G; o < 32; o <<= 1)
 #pragma unroll
@@ -329,13 +426,20 @@ __global__ void __launch_bounds__(512) attention_kernel(const AttentionArgs a) {
   }
 }
 
-// Queue 2: light rows of fewer than 32 edges.  A warp grabs 32 of them, reads ids and row pointers
-// with coalesced loads and walks them with the next row's columns already in flight; one batch per
-// row, so the online-softmax state never needs rescaling.  A kernel of its own (72 registers against
-// the main kernel's 128, so more warps in flight for these latency-bound rows), launched as a
-// programmatic dependent of the main kernel: it fills the SMs while the longest hub rows finish.
-template <int VW, int G, int NV, int U>
+// Queue 2: light rows of fewer than 32 edges - nine rows in ten of a power-law graph, and bound by the
+// chain of dependent memory round trips (row pointers -> columns -> K rows -> V rows -> output), not by
+// bandwidth.  A warp grabs 32 of them (ids and row pointers with one coalesced load each) and walks
+// them 32/G rows at a time: each group of G lanes - the lanes that together hold one feature row - owns
+// a row of its own, reads that row's columns itself, and for every edge fetches the K row AND the V
+// row in the same step (the V row does not depend on the score), EDGES edges per step; scores, running
+// maximum, running sum and the rescaled accumulator then stay inside the group, so nothing is reduced
+// across groups and every group stores its own output row.  The columns of the next rows are fetched
+// while the current ones are gathered.  A kernel of its own, launched as a programmatic dependent of
+// the main kernel: it fills the SMs while the longest hub rows finish.
+template <int VW, int G, int NV, int EDGES>
 __global__ void __launch_bounds__(512) attention_short_kernel(const AttentionArgs a) {
+  constexpr int RPW = 32 / G;                      // rows a warp processes side by side
+  constexpr int CREG = (kShortDegree + G - 1) / G;  // column registers per lane: G columns each
   const int lane = threadIdx.x & 31;
   const int l = lane % G;
   const int sub = lane / G;
@@ -348,30 +452,63 @@ __global__ void __launch_bounds__(512) attention_short_kernel(const AttentionArg
   if (n_short > 0) {
     const int* shorts = a.order + n_hub + n_medium;
     const int n_batches = (n_short + 31) / 32;
+    bool fvalid[NV];
+    int foff[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      foff[v] = VW * (l + G * v);
+      fvalid[v] = foff[v] < f;
+    }
     for (;;) {
       const unsigned long long it = warp_next(&a.header->counter[2]);
       if (it >= static_cast<unsigned long long>(n_batches)) break;
       const int first = static_cast<int>(it) * 32;
       const int n_here = n_short - first < 32 ? n_short - first : 32;
       int row_l = 0;
-      long long s_l = 0, e_l = 0;
+      long long s_l = 0;
+      int d_l = 0;
       if (lane < n_here) {
         row_l = shorts[first + lane];
         s_l = a.crow[row_l];
-        e_l = a.crow[row_l + 1];
+        d_l = static_cast<int>(a.crow[row_l + 1] - s_l);
       }
-      long long s_cur = __shfl_sync(kFull, s_l, 0);
-      int cnt_cur = static_cast<int>(__shfl_sync(kFull, e_l, 0) - s_cur);
-      int c_next = 0;
-      if (lane < cnt_cur) c_next = static_cast<int>(ld_index(a.col + s_cur + lane, pol_stream));
-      for (int r = 0; r < n_here; ++r) {
-        const int row = __shfl_sync(kFull, row_l, r);
-        const int cnt = cnt_cur;
-        const int c_l = c_next;
-        if (r + 1 < n_here) {
-          s_cur = __shfl_sync(kFull, s_l, r + 1);
-          cnt_cur = static_cast<int>(__shfl_sync(kFull, e_l, r + 1) - s_cur);
-          if (lane < cnt_cur) c_next = static_cast<int>(ld_index(a.col + s_cur + lane, pol_stream));
+      // columns of the first rows: lane l of a group holds columns l, l + G, ... of the group's row
+      int c_next[CREG];
+      {
+        const long long s0 = __shfl_sync(kFull, s_l, sub);
+        const int d0 = __shfl_sync(kFull, d_l, sub);
+#pragma unroll
+        for (int k = 0; k < CREG; ++k)
+          c_next[k] = (l + k * G < d0) ? static_cast<int>(ld_index(a.col + s0 + l + k * G, pol_stream)) : 0;
+      }
+      for (int r0 = 0; r0 < n_here; r0 += RPW) {
+        const int mine = r0 + sub;                      // this group's row of the batch (may be past the end)
+        const int src = mine < 32 ? mine : 31;
+        const int row = __shfl_sync(kFull, row_l, src);
+        const int cnt = mine < n_here ? __shfl_sync(kFull, d_l, src) : 0;
+        int c_cur[CREG];
+#pragma unroll
+        for (int k = 0; k < CREG; ++k) c_cur[k] = c_next[k];
+        if (r0 + RPW < n_here) {  // warp-uniform
+          const int ahead = r0 + RPW + sub < 32 ? r0 + RPW + sub : 31;
+          const long long s1 = __shfl_sync(kFull, s_l, ahead);
+          const int d1 = r0 + RPW + sub < n_here ? __shfl_sync(kFull, d_l, ahead) : 0;
+#pragma unroll
+          for (int k = 0; k < CREG; ++k)
+            c_next[k] = (l + k * G < d1) ? static_cast<int>(ld_index(a.col + s1 + l + k * G, pol_stream)) : 0;
+        }
+        float q[NV][VW];
+        if (cnt > 0) {
+          const float* qrow = a.q + static_cast<size_t>(row) * f;
+#pragma unroll
+          for (int v = 0; v < NV; ++v) {
+            if (fvalid[v]) {
+              VecIO<VW>::load(q[v], qrow + foff[v], pol_stream);
+            } else {
+#pragma unroll
+              for (int i = 0; i < VW; ++i) q[v][i] = 0.f;
+            }
+          }
         }
         float m_run = -CUDART_INF_F, l_run = 0.f;
         float acc[NV][VW];
@@ -379,29 +516,75 @@ __global__ void __launch_bounds__(512) attention_short_kernel(const AttentionArg
         for (int v = 0; v < NV; ++v)
 #pragma unroll
           for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
-        if (cnt > 0) {
-          float q[NV][VW];
-          bool fvalid[NV];
-          int foff[NV];
-          attention_load_q<VW, G, NV>(a, row, lane, pol_stream, q, fvalid, foff);
-          attention_one_batch<VW, G, NV, U>(a, c_l, cnt, lane, q, fvalid, foff, pol_keep, m_run, l_run, acc);
+        const int longest = __reduce_max_sync(kFull, cnt);  // the shuffles below need every lane
+        for (int j = 0; j < longest; j += EDGES) {
+          float kv[EDGES][NV][VW], vv[EDGES][NV][VW];
+          bool ok[EDGES];
 #pragma unroll
-          for (int o = G; o < 32; o <<= 1)
+          for (int u = 0; u < EDGES; ++u) {
+            const int e = j + u;
+            int c = 0;
+#pragma unroll
+            for (int k = 0; k < CREG; ++k) {
+              const int got = __shfl_sync(kFull, c_cur[k], sub * G + ((e - k * G) & (G - 1)));
+              if (e >= k * G && e < (k + 1) * G) c = got;
+            }
+            ok[u] = e < cnt;
+            const float* krow = a.k + static_cast<size_t>(c) * f;
+            const float* vrow = a.v + static_cast<size_t>(c) * f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+              if (ok[u] && fvalid[v]) {
+                VecIO<VW>::load(kv[u][v], krow + foff[v], pol_keep);
+                VecIO<VW>::load(vv[u][v], vrow + foff[v], pol_keep);
+              } else {
+#pragma unroll
+                for (int i = 0; i < VW; ++i) kv[u][v][i] = vv[u][v][i] = 0.f;
+              }
+            }
+          }
+          float score[EDGES];
+          float m_new = m_run;
+#pragma unroll
+          for (int u = 0; u < EDGES; ++u) {
+            float d = 0.f;
 #pragma unroll
             for (int v = 0; v < NV; ++v)
 #pragma unroll
-              for (int i = 0; i < VW; ++i) acc[v][i] += __shfl_xor_sync(kFull, acc[v][i], o);
+              for (int i = 0; i < VW; ++i) d = fmaf(q[v][i], kv[u][v][i], d);
+#pragma unroll
+            for (int o = G / 2; o >= 1; o >>= 1) d += __shfl_xor_sync(kFull, d, o);  // stays inside the group
+            score[u] = ok[u] ? d * a.scale : -CUDART_INF_F;
+            m_new = fmaxf(m_new, score[u]);
+          }
+          if (m_new > -CUDART_INF_F) {  // this group still has edges in the step
+            const float rescale = expf(m_run - m_new);  // exp(-inf) = 0 on the first step
+            l_run *= rescale;
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+              for (int i = 0; i < VW; ++i) acc[v][i] *= rescale;
+#pragma unroll
+            for (int u = 0; u < EDGES; ++u) {
+              const float p = ok[u] ? expf(score[u] - m_new) : 0.f;
+              l_run += p;
+#pragma unroll
+              for (int v = 0; v < NV; ++v)
+#pragma unroll
+                for (int i = 0; i < VW; ++i) acc[v][i] = fmaf(p, vv[u][v][i], acc[v][i]);
+            }
+            m_run = m_new;
+          }
         }
-        if (sub == 0) {
+        if (mine < n_here) {
           const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll
           for (int v = 0; v < NV; ++v) {
-            const int fo = VW * (l + G * v);
-            if (fo < f) {
+            if (fvalid[v]) {
               float out_v[VW];
 #pragma unroll
               for (int i = 0; i < VW; ++i) out_v[i] = acc[v][i] * inv;
-              VecIO<VW>::store(a.out + static_cast<size_t>(row) * f + fo, out_v);
+              VecIO<VW>::store(a.out + static_cast<size_t>(row) * f + foff[v], out_v);
             }
           }
         }
@@ -422,9 +605,15 @@ static int launch_attention_instance(const AttentionArgs& args, int warps, cudaS
   int per_sm = 0;
   ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem));
   if (per_sm < 1) per_sm = 1;
+  if (args.split != nullptr) {  // every call: the completion counters start from zero
+    attention_split_plan<<<1, 1, 0, stream>>>(args);
+    ASG_CUDA(cudaGetLastError());
+  }
   kernel<<<sm_count(device) * per_sm, threads, smem, stream>>>(args);
   ASG_CUDA(cudaGetLastError());
-  auto short_kernel = attention_short_kernel<VW, G, NV, U>;
+  // edges gathered per step in the short-row kernel: K and V rows of 4 edges (2 when a lane already
+  // holds more than one vector per row) keep the kernel under 128 registers
+  auto short_kernel = attention_short_kernel<VW, G, NV, (NV > 1 ? 2 : 4)>;
   int short_per_sm = 0;
   ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&short_per_sm, short_kernel, threads, 0));
   if (short_per_sm < 1) short_per_sm = 1;
@@ -499,9 +688,14 @@ int asg_csr_row_softmax(const int64_t* crow, const float* scores, float* probs, 
   return ASG_OK;
 }
 
+size_t asg_attention_workspace_bytes(int64_t n_rows) {
+  if (n_rows < 0) n_rows = 0;
+  return asg::workspace_bytes(n_rows) + sizeof(asg::SplitArea);
+}
+
 int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, const float* k, const float* v,
                       float* out, int64_t n_rows, int64_t nnz, int64_t f, float scale, int warps_per_block,
-                      int64_t hub_threshold, unsigned flags, void* workspace, size_t workspace_bytes,
+                      int64_t hub_threshold, unsigned flags, void* workspace, size_t workspace_size,
                       void* stream_ptr) {
   using namespace asg;
   ASG_REQUIRE(n_rows >= 0 && nnz >= 0 && f >= 0, ASG_EINVAL, "sizes must be non-negative");
@@ -513,7 +707,7 @@ int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, c
   ASG_REQUIRE(crow != nullptr && q != nullptr && k != nullptr && v != nullptr && out != nullptr, ASG_EINVAL,
               "crow, query, key, value and out must not be null");
   ASG_REQUIRE(nnz == 0 || col != nullptr, ASG_EINVAL, "col must not be null");
-  if (int rc = check_workspace(workspace, workspace_bytes, n_rows)) return rc;
+  if (int rc = check_workspace(workspace, workspace_size, n_rows)) return rc;
   DeviceGuard guard(out);
   ASG_CUDA(guard.status);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
@@ -538,6 +732,11 @@ int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, c
   args.out = out;
   args.header = static_cast<Header*>(workspace);
   args.order = reinterpret_cast<const int*>(static_cast<const char*>(workspace) + order_offset());
+  // the split area is used when the caller's workspace has room for it (asg_attention_workspace_bytes)
+  const size_t split_at = workspace_bytes(n_rows);
+  args.split = workspace_size >= split_at + sizeof(SplitArea)
+                   ? reinterpret_cast<SplitArea*>(static_cast<char*>(workspace) + split_at)
+                   : nullptr;
   args.f = static_cast<int>(f);
   args.scale = scale;
   return launch_attention(args, vw, warps_per_block, stream, guard.target);

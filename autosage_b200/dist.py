@@ -114,6 +114,31 @@ def column_groups(rank: int, world: int, groups=None) -> list[list[int]]:
     return out
 
 
+def split_edges_by_group(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor], group: torch.Tensor,
+                         n_groups: int, labels: Optional[list[int]] = None) -> list[ColumnBlock]:
+    """Stable partition of a CSR's edges by ``group[e]`` (int64, one entry per edge): block g is a CSR
+    over the same rows holding the edges of group g in their original order.  ``labels[g]`` becomes the
+    block's ``owner`` field (default g)."""
+    n_local = crow.numel() - 1
+    device = col.device
+    degrees = crow[1:] - crow[:-1]
+    rows = torch.repeat_interleave(torch.arange(n_local, device=device, dtype=torch.long), degrees)
+    order = torch.argsort(group * max(n_local, 1) + rows, stable=True)
+    per_group = torch.bincount(group[order], minlength=n_groups).cpu().tolist()
+    blocks: list[ColumnBlock] = []
+    start = 0
+    for g in range(n_groups):
+        stop = start + per_group[g]
+        picked = order[start:stop]
+        counts = torch.bincount(rows[picked], minlength=n_local)
+        block_crow = torch.zeros(n_local + 1, dtype=torch.long, device=device)
+        torch.cumsum(counts, 0, out=block_crow[1:])
+        blocks.append(ColumnBlock(g if labels is None else labels[g], block_crow, col[picked].contiguous(),
+                                  None if val is None else val[picked].contiguous()))
+        start = stop
+    return blocks
+
+
 def split_columns_by_owner(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor],
                            bounds: torch.Tensor, groups: Optional[list[list[int]]] = None) -> list[ColumnBlock]:
     """Stable partition of a CSR's edges by the group of owner(col), owner k holding columns
@@ -123,7 +148,6 @@ def split_columns_by_owner(crow: torch.Tensor, col: torch.Tensor, val: Optional[
     world = bounds.numel() - 1
     if groups is None:
         groups = [[k] for k in range(world)]
-    n_local = crow.numel() - 1
     device = col.device
     cuts = bounds[1:-1].to(device)
     owner = torch.bucketize(col, cuts, right=True) if world > 1 else torch.zeros_like(col)
@@ -131,23 +155,61 @@ def split_columns_by_owner(crow: torch.Tensor, col: torch.Tensor, val: Optional[
     for g, members in enumerate(groups):
         for k in members:
             group_of[k] = g
-    group = group_of.to(device)[owner]
-    degrees = crow[1:] - crow[:-1]
-    rows = torch.repeat_interleave(torch.arange(n_local, device=device, dtype=torch.long), degrees)
-    order = torch.argsort(group * max(n_local, 1) + rows, stable=True)
-    per_group = torch.bincount(group[order], minlength=len(groups)).cpu().tolist()
-    blocks: list[ColumnBlock] = []
-    start = 0
-    for g, members in enumerate(groups):
-        stop = start + per_group[g]
-        picked = order[start:stop]
-        counts = torch.bincount(rows[picked], minlength=n_local)
-        block_crow = torch.zeros(n_local + 1, dtype=torch.long, device=device)
-        torch.cumsum(counts, 0, out=block_crow[1:])
-        blocks.append(ColumnBlock(members[-1], block_crow, col[picked].contiguous(),
-                                  None if val is None else val[picked].contiguous()))
-        start = stop
-    return blocks
+    return split_edges_by_group(crow, col, val, group_of.to(device)[owner], len(groups),
+                                labels=[members[-1] for members in groups])
+
+
+class GatherLayout:
+    """Where row g of the gathered operand lives in a rank's buffer when the exchange moves CHUNKS of
+    every shard at once (one collective, or one push, per chunk) instead of one owner's shard at a time.
+
+    Shards are cut into ``chunks`` pieces of ``chunk_rows`` rows (the last piece of a shard may be
+    shorter or empty; shards are padded to ``chunks * chunk_rows`` rows).  The buffer holds, chunk after
+    chunk, that chunk of every owner in owner order:
+        position(owner k, local row i) = (i // chunk_rows) * world * chunk_rows + k * chunk_rows + i % chunk_rows
+    so chunk c of all owners is the contiguous slice ``chunk_view(buffer, c)`` - the output of one
+    all-gather whose per-rank input is ``own_view(buffer, c, rank)``, a slice of that output."""
+
+    def __init__(self, bounds: torch.Tensor, chunks: int) -> None:
+        self.bounds = bounds.to(torch.long).cpu()
+        self.world = self.bounds.numel() - 1
+        self.chunks = max(1, int(chunks))
+        longest = int((self.bounds[1:] - self.bounds[:-1]).max()) if self.world else 0
+        self.chunk_rows = max(1, -(-longest // self.chunks))
+        self.rows_total = self.chunks * self.world * self.chunk_rows
+
+    def owner_and_local(self, rows: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        cuts = self.bounds[1:-1].to(rows.device)
+        owner = torch.bucketize(rows, cuts, right=True) if self.world > 1 else torch.zeros_like(rows)
+        return owner, rows - self.bounds.to(rows.device)[owner]
+
+    def position(self, rows: torch.Tensor) -> torch.Tensor:
+        """Buffer positions of the global row ids ``rows`` (any device)."""
+        owner, local = self.owner_and_local(rows)
+        chunk = torch.div(local, self.chunk_rows, rounding_mode="floor")
+        return chunk * (self.world * self.chunk_rows) + owner * self.chunk_rows + (local - chunk * self.chunk_rows)
+
+    def chunk_of(self, rows: torch.Tensor) -> torch.Tensor:
+        return torch.div(self.owner_and_local(rows)[1], self.chunk_rows, rounding_mode="floor")
+
+    def chunk_view(self, buffer: torch.Tensor, chunk: int) -> torch.Tensor:
+        span = self.world * self.chunk_rows
+        return buffer[chunk * span:(chunk + 1) * span]
+
+    def own_view(self, buffer: torch.Tensor, chunk: int, rank: int) -> torch.Tensor:
+        begin = chunk * self.world * self.chunk_rows + rank * self.chunk_rows
+        return buffer[begin:begin + self.chunk_rows]
+
+    def local_pieces(self, rank: int) -> list[tuple[int, int, int]]:
+        """(first local row, number of rows, buffer position) of the pieces of rank's own shard."""
+        n_local = int(self.bounds[rank + 1] - self.bounds[rank])
+        pieces = []
+        for chunk in range(self.chunks):
+            first = chunk * self.chunk_rows
+            count = min(self.chunk_rows, n_local - first)
+            if count > 0:
+                pieces.append((first, count, chunk * self.world * self.chunk_rows + rank * self.chunk_rows))
+        return pieces
 
 
 def shard_csr(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor], rank: int, world: int,
@@ -208,11 +270,18 @@ class ShardedSpmm:
               SMs, so the column-block SpMMs keep the whole GPU.  One barrier before the pulls (all
               shards written) and one after (all pulls done, shards may be overwritten).
       "nccl"  P-1 grouped isend/irecv steps; also the path of the CPU/gloo tests.
+      "allgather"  the collective itself: ``chunks`` calls of all_gather_into_tensor (NCCL picks its own
+              algorithm, NVLS included), chunk c of every shard at once, in the padded chunk-major layout
+              of ``GatherLayout``.  Column blocks are then "own columns" (no wait) plus one per chunk.
+      "push"  SM-driven: every rank stores chunk c of its own shard into all peers' buffers with plain
+              128-bit stores (``asg_push_to_peers``, ``push_ctas`` CTAs), a symmetric-memory barrier after
+              every chunk; same layout and column blocks as "allgather".
     """
 
     def __init__(self, shard: RowShard, features: int, *, group=None, dtype=torch.float32, feature_tile: int = 128,
                  warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
-                 exchange: Optional[str] = None, copy_streams: int = 1, slabs: int = 0) -> None:
+                 exchange: Optional[str] = None, copy_streams: int = 1, slabs: int = 0, chunks: int = 2,
+                 push_ctas: int = 32) -> None:
         self.shard = shard
         self.group = group
         self.features = features
@@ -227,12 +296,24 @@ class ShardedSpmm:
                              if device.type == "cuda" else [])
         self.handle = None
         self.x_full = None
+        self.layout: Optional[GatherLayout] = None
+        self.push_ctas = int(push_ctas)
         wanted = exchange or os.getenv("AUTOSAGE_EXCHANGE", "peer" if device.type == "cuda" else "nccl")
-        if wanted == "peer" and device.type == "cuda" and shard.world > 1:
-            self._try_symmetric(dtype)
-        if self.x_full is None:
-            self.x_full = torch.empty(shard.n_global, features, dtype=dtype, device=device)
-        self.exchange = "peer" if self.handle is not None else "nccl"
+        if wanted in ("allgather", "push") and shard.world > 1:
+            self.layout = GatherLayout(shard.bounds, chunks)
+            if wanted == "push" and device.type == "cuda":
+                self._try_symmetric(dtype, rows=self.layout.rows_total)
+            if self.x_full is None:
+                self.x_full = torch.empty(self.layout.rows_total, features, dtype=dtype, device=device)
+            self.exchange = "push" if self.handle is not None else "allgather"
+            self._chunk_blocks = self._build_chunk_blocks()
+            self._chunk_events = [torch.cuda.Event() for _ in range(self.layout.chunks)] if device.type == "cuda" else []
+        else:
+            if wanted == "peer" and device.type == "cuda" and shard.world > 1:
+                self._try_symmetric(dtype)
+            if self.x_full is None:
+                self.x_full = torch.empty(shard.n_global, features, dtype=dtype, device=device)
+            self.exchange = "peer" if self.handle is not None else "nccl"
         if not shard.groups:
             shard.groups = [[k] for k in arrival_order(shard.rank, shard.world)]
         # Feature-slab mode (peer exchange only): X is pulled in `slabs` bands of feature columns, band s
@@ -267,21 +348,26 @@ class ShardedSpmm:
                     sums.setdefault(name, []).append(marks["start"].elapsed_time(event))
         return {name: round(sum(v) / len(v), 4) for name, v in sums.items()}
 
-    def _try_symmetric(self, dtype) -> None:
-        """Allocate X in symmetric memory and map the peers' copies; all ranks agree on the outcome."""
+    def _try_symmetric(self, dtype, rows: Optional[int] = None) -> None:
+        """Allocate X in symmetric memory and map the peers' copies; all ranks agree on the outcome.
+        With ``rows`` (chunked layouts) each peer's WHOLE buffer is mapped, else only the peer's own shard."""
         ok = 1
         try:
             import torch.distributed._symmetric_memory as symm
 
             pg = self.group if self.group is not None else dist.group.WORLD
-            buffer = symm.empty((self.shard.n_global, self.features), dtype=dtype, device=self.device)
+            total = self.shard.n_global if rows is None else rows
+            buffer = symm.empty((total, self.features), dtype=dtype, device=self.device)
             handle = symm.rendezvous(buffer, pg)
             peers = {}
             b = self.shard.bounds
             for owner in range(self.shard.world):
                 if owner != self.shard.rank:
-                    rows = int(b[owner + 1]) - int(b[owner])
-                    peers[owner] = handle.get_buffer(owner, (rows, self.features), dtype, int(b[owner]) * self.features)
+                    if rows is None:
+                        count = int(b[owner + 1]) - int(b[owner])
+                        peers[owner] = handle.get_buffer(owner, (count, self.features), dtype, int(b[owner]) * self.features)
+                    else:
+                        peers[owner] = handle.get_buffer(owner, (total, self.features), dtype, 0)
         except Exception as exc:  # noqa: BLE001 - any failure means "use NCCL send/recv instead"
             self._symmetric_error = exc
             ok = 0
@@ -292,8 +378,58 @@ class ShardedSpmm:
 
     @property
     def x_local(self) -> torch.Tensor:
-        """View of the rank's own rows inside the gathered buffer: write the shard's features here."""
+        """View of the rank's own rows inside the gathered buffer: write the shard's features here.
+        (Chunked layouts keep the shard in several pieces: use ``load_local`` there.)"""
+        if self.layout is not None:
+            raise RuntimeError("the chunked layout has no single view of the local rows; use load_local()")
         return self.x_full[self.shard.row_begin:self.shard.row_end]
+
+    def load_local(self, features: torch.Tensor, non_blocking: bool = False) -> None:
+        """Copy this rank's feature rows (``[n_local, F]``, any device) into the gathered buffer."""
+        if self.layout is None:
+            if features.data_ptr() != self.x_local.data_ptr():
+                self.x_local.copy_(features, non_blocking=non_blocking)
+            return
+        for first, count, position in self.layout.local_pieces(self.shard.rank):
+            self.x_full[position:position + count].copy_(features[first:first + count], non_blocking=non_blocking)
+
+    def _build_chunk_blocks(self) -> list[ColumnBlock]:
+        """Chunked layouts: block 0 holds the edges into this rank's own columns, block 1 + c the edges
+        into the other ranks' columns of chunk c; column ids become positions in the gathered buffer."""
+        shard, layout = self.shard, self.layout
+        owner, local = layout.owner_and_local(shard.col)
+        chunk = torch.div(local, layout.chunk_rows, rounding_mode="floor")
+        group = torch.where(owner == shard.rank, torch.zeros_like(chunk), chunk + 1)
+        return split_edges_by_group(shard.crow, layout.position(shard.col), shard.val, group, layout.chunks + 1)
+
+    def _start_chunk_exchange(self) -> None:
+        """Chunked layouts, on the communication stream (CPU: inline): chunk after chunk of every shard,
+        an event after each."""
+        shard, layout = self.shard, self.layout
+        if self.exchange == "push":
+            main = self.comm_stream
+            self.handle.barrier(channel=0)  # every rank is done reading the previous contents
+            self._mark("pulls_begin", main)
+            others = [owner for owner in arrival_order(shard.rank, shard.world)[1:]]
+            for c in range(layout.chunks):
+                own = layout.own_view(self.x_full, c, shard.rank)
+                _native.push_to_peers(own, [layout.own_view(self._peers[o], c, shard.rank) for o in others], self.push_ctas)
+                self.handle.barrier(channel=0)  # all ranks' stores of this chunk have completed
+                self._chunk_events[c].record(main)
+            self._mark("pulls_end", main)
+            return
+        for c in range(layout.chunks):
+            whole, own = layout.chunk_view(self.x_full, c), layout.own_view(self.x_full, c, shard.rank)
+            if self.comm_stream is None:
+                dist.all_gather_into_tensor(whole.view(-1), own.reshape(-1), group=self.group)
+                continue
+            if c == 0:
+                self._mark("pulls_begin", self.comm_stream)
+            work = dist.all_gather_into_tensor(whole.view(-1), own.view(-1), group=self.group, async_op=True)
+            work.wait()  # the communication stream (current here) waits for the collective; the host does not
+            self._chunk_events[c].record(self.comm_stream)
+        if self.comm_stream is not None:
+            self._mark("pulls_end", self.comm_stream)
 
     def _shard_view(self, owner: int) -> torch.Tensor:
         b = self.shard.bounds
@@ -381,6 +517,16 @@ class ShardedSpmm:
         """Runs just the gather of X (for measurements); the current stream waits for its end."""
         if self.shard.world == 1:
             return
+        if self.layout is not None:
+            if self.comm_stream is None:
+                self._start_chunk_exchange()
+                return
+            current = torch.cuda.current_stream(self.device)
+            self.comm_stream.wait_stream(current)
+            with torch.cuda.stream(self.comm_stream):
+                self._start_chunk_exchange()
+            current.wait_stream(self.comm_stream)
+            return
         if self.exchange == "peer":
             current = torch.cuda.current_stream(self.device)
             self.comm_stream.wait_stream(current)
@@ -413,6 +559,27 @@ class ShardedSpmm:
         if shard.world == 1:
             _block_spmm(shard.blocks[0], self.x_full, y, False, **kw)
             self._mark("spmm_end")
+            return y
+
+        if self.layout is not None:
+            blocks = self._chunk_blocks
+            if self.comm_stream is None:  # CPU ranks: exchange first, then the products
+                self._start_chunk_exchange()
+                for g, block in enumerate(blocks):
+                    _block_spmm(block, self.x_full, y, g > 0, **kw)
+                return y
+            current = torch.cuda.current_stream(self.device)
+            self.comm_stream.wait_stream(current)
+            with torch.cuda.stream(self.comm_stream):
+                self._start_chunk_exchange()
+            if not overlap:
+                current.wait_stream(self.comm_stream)
+            for g, block in enumerate(blocks):
+                if overlap and g > 0:
+                    current.wait_event(self._chunk_events[g - 1])
+                _block_spmm(block, self.x_full, y, g > 0, **kw)
+                self._mark(f"block{g}_end")
+            current.wait_stream(self.comm_stream)
             return y
 
         if self.exchange == "peer" and self.slabs:
@@ -489,8 +656,8 @@ class _GatheredOperand:
         return self._engine.exchange
 
     def gather(self, local: Optional[torch.Tensor]) -> torch.Tensor:
-        if local is not None and local.data_ptr() != self.local.data_ptr():
-            self.local.copy_(local)
+        if local is not None:
+            self._engine.load_local(local)
         self._engine.exchange_only()
         return self.full
 
@@ -569,7 +736,8 @@ class ShardedAttention:
         if out.numel() == 0:
             return out
         if self._workspace is None:
-            self._workspace = torch.empty(_native.workspace_bytes(shard.n_local), dtype=torch.uint8, device=query.device)
+            self._workspace = torch.empty(_native.workspace_bytes(shard.n_local) + _native.attention_extra_bytes(shard.n_local),
+                                          dtype=torch.uint8, device=query.device)
         _native.attention(shard.crow, shard.col, query, key_full, value_full, out, scale=float(scale), warps=self.warps,
                           threshold=self.threshold, flags=_native.FLAG_PLAN_READY if self._plan_ready else 0,
                           workspace=self._workspace)
@@ -582,11 +750,13 @@ class ShardedAutoSAGEConv(torch.nn.Module):
 
     def __init__(self, shard: RowShard, in_channels: int, out_channels: int, *, bias: bool = True, group=None,
                  feature_tile: int = 128, warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
-                 exchange: Optional[str] = None, copy_streams: int = 1, slabs: int = 0) -> None:
+                 exchange: Optional[str] = None, copy_streams: int = 1, slabs: int = 0, chunks: int = 2,
+                 push_ctas: int = 32) -> None:
         super().__init__()
         self.linear = torch.nn.Linear(in_channels, out_channels, bias=bias)
         self.spmm = ShardedSpmm(shard, in_channels, group=group, feature_tile=feature_tile, warps=warps,
-                                threshold=threshold, exchange=exchange, copy_streams=copy_streams, slabs=slabs)
+                                threshold=threshold, exchange=exchange, copy_streams=copy_streams, slabs=slabs,
+                                chunks=chunks, push_ctas=push_ctas)
 
     def capture(self, warmup: int = 2):
         """Captures one inference forward (features already in ``spmm.x_local``) into a CUDA graph and
@@ -597,7 +767,7 @@ class ShardedAutoSAGEConv(torch.nn.Module):
         is 2-3 ms of GPU work and the eager launch sequence does not always stay ahead of it.  All
         ranks must call this together; if any rank fails to capture, all return None (run eagerly)."""
         spmm = self.spmm
-        if spmm.device.type != "cuda" or (spmm.shard.world > 1 and spmm.exchange != "peer"):
+        if spmm.device.type != "cuda" or (spmm.shard.world > 1 and spmm.exchange == "nccl"):
             return None  # the send/recv exchange is driven from the host (work.wait()), step by step
         ok = 1
         graph, out = None, None
@@ -627,8 +797,8 @@ class ShardedAutoSAGEConv(torch.nn.Module):
         return replay
 
     def forward(self, x_local: Optional[torch.Tensor] = None, overlap: bool = True) -> torch.Tensor:
-        if x_local is not None and x_local.data_ptr() != self.spmm.x_local.data_ptr():
-            self.spmm.x_local.copy_(x_local)
+        if x_local is not None:
+            self.spmm.load_local(x_local)
         spmm = self.spmm
         differentiating = torch.is_grad_enabled() and any(p.requires_grad for p in self.linear.parameters())
         if not spmm.slabs or spmm.shard.world == 1 or differentiating:

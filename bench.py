@@ -240,7 +240,7 @@ def run_ours_single(args) -> dict:
     else:
         q, k, v = w["q"], w["k"], w["v"]
         out = torch.empty(n, f, device=device)
-        ws, _ = _native.planned_workspace(crow, threshold)
+        ws, _ = _native.planned_workspace(crow, threshold, _native.attention_extra_bytes(n))
         _native.plan_build(crow, threshold, ws)
         scale = f ** -0.5
 
@@ -255,7 +255,7 @@ def run_ours_single(args) -> dict:
         def e2e_step(dev_inputs):
             c, cc, qq, kk, vv = dev_inputs
             o = torch.empty_like(vv)
-            w2, ready = _native.planned_workspace(c, threshold)
+            w2, ready = _native.planned_workspace(c, threshold, _native.attention_extra_bytes(c.numel() - 1))
             _native.attention(c, cc, qq, kk, vv, o, scale=scale, warps=warps, threshold=threshold, flags=ready,
                               workspace=w2)
             return o
@@ -640,7 +640,10 @@ def main() -> None:
     parser.add_argument("--copy-streams", type=int, default=1, help="streams used for the peer pulls (sharded path)")
     parser.add_argument("--no-graph", action="store_true",
                         help="sharded path: launch every step eagerly instead of replaying a CUDA graph")
-    parser.add_argument("--exchange", default=None, choices=["peer", "nccl"], help="how X is gathered (sharded path)")
+    parser.add_argument("--exchange", default=None, choices=["peer", "nccl", "allgather", "push"],
+                        help="how X is gathered (sharded path)")
+    parser.add_argument("--chunks", type=int, default=2, help="chunks of the allgather / push exchange")
+    parser.add_argument("--push-ctas", type=int, default=32, help="CTAs of the SM-driven push")
     args = parser.parse_args()
     if args.groups is not None:
         args.groups = [int(v) for v in args.groups.split(",")] if "," in args.groups else int(args.groups)

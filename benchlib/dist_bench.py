@@ -17,6 +17,14 @@ import torch
 import torch.distributed as dist
 
 
+EXCHANGE_NAMES = {
+    "peer": "copy-engine pulls from peer memory",
+    "nccl": "NCCL send/recv steps",
+    "allgather": "NCCL all_gather_into_tensor per chunk",
+    "push": "SM-driven 128-bit stores into peer memory per chunk",
+}
+
+
 def conv_bytes(n_rows: int, nnz: int, f: int, out_f: int) -> int:
     spmm = 8 * (n_rows + 1) + 8 * nnz + 4 * nnz * f + 4 * n_rows * f
     linear = 4 * n_rows * f + 4 * n_rows * out_f
@@ -248,7 +256,7 @@ def run(args):
         whole = asg_dist.shard_csr(crow, col, None, 0, 1, asg_dist.partition_rows(crow, 1))
         solo = seeded(asg_dist.ShardedAutoSAGEConv(whole, f, out_f, bias=True, feature_tile=args.tile, warps=args.warps,
                                                    threshold=args.hub_threshold).to(device))
-        solo.spmm.x_local.copy_(x_all)
+        solo.spmm.load_local(x_all)
         with torch.no_grad():
             for _ in range(3):
                 solo()
@@ -270,10 +278,11 @@ def run(args):
 
     layer = seeded(asg_dist.ShardedAutoSAGEConv(shard, f, out_f, bias=True, feature_tile=args.tile, warps=args.warps,
                                                 threshold=args.hub_threshold, exchange=args.exchange,
-                                                copy_streams=args.copy_streams, slabs=args.slabs).to(device))
+                                                copy_streams=args.copy_streams, slabs=args.slabs, chunks=args.chunks,
+                                                push_ctas=args.push_ctas).to(device))
     pinning = bind_to_gpu_numa_node(local_rank) if multi else None  # before any pinned buffer is allocated
     x_shard_host = x_all[shard.row_begin:shard.row_end].cpu().pin_memory()
-    layer.spmm.x_local.copy_(x_all[shard.row_begin:shard.row_end])
+    layer.spmm.load_local(x_all[shard.row_begin:shard.row_end])
     del x_all
     torch.cuda.empty_cache()
 
@@ -353,7 +362,8 @@ def run(args):
             layer.spmm._slab_products(aggregated_scratch, None)
             return
         kw = dict(feature_tile=args.tile, warps=args.warps, threshold=args.hub_threshold)
-        for g, block in enumerate(shard.blocks):
+        blocks = layer.spmm._chunk_blocks if layer.spmm.layout is not None else shard.blocks
+        for g, block in enumerate(blocks):
             asg_dist._block_spmm(block, layer.spmm.x_full, aggregated_scratch, g > 0, **kw)
 
     # timeline of a few more (untimed) steps: mean offsets of the exchange and compute marks from the
@@ -406,7 +416,7 @@ def run(args):
     drain = torch.cuda.Stream(device=device)
 
     def e2e_serial_step():
-        layer.spmm.x_local.copy_(x_shard_host, non_blocking=True)
+        layer.spmm.load_local(x_shard_host, non_blocking=True)
         out_host.copy_(step(), non_blocking=True)
 
     # a replayed graph writes the same output buffer every step: stage it in one of two device
@@ -415,7 +425,7 @@ def run(args):
     drained: list = [None, None]
 
     def e2e_streamed_step(i):
-        layer.spmm.x_local.copy_(x_shard_host, non_blocking=True)
+        layer.spmm.load_local(x_shard_host, non_blocking=True)
         out = step()
         if staged is not None:
             if drained[i % 2] is not None:
@@ -469,7 +479,7 @@ def run(args):
 
     last_out = step()
     pcie = {
-        "h2d_GBps_per_rank_min_max": copy_rate(lambda: layer.spmm.x_local.copy_(x_shard_host, non_blocking=True),
+        "h2d_GBps_per_rank_min_max": copy_rate(lambda: layer.spmm.load_local(x_shard_host, non_blocking=True),
                                                x_shard_host.numel() * 4),
         "d2h_GBps_per_rank_min_max": copy_rate(lambda: out_host.copy_(last_out, non_blocking=True), out_host.numel() * 4),
         "numa": pinning,
@@ -483,6 +493,7 @@ def run(args):
     else:
         gathered = [local_nnz]
 
+    n_blocks = len(layer.spmm._chunk_blocks) if layer.spmm.layout is not None else len(shard.blocks)
     algorithmic = conv_bytes(n, nnz, f, out_f)
     value = algorithmic / (ms_per_step * 1e-3) / 1e9
     peak, peak_kind = bench.measured_peak()
@@ -540,8 +551,8 @@ def run(args):
             "config": {
                 "workload": bench.conv_workload_label(n, nnz, f, out_f),
                 "parallelism": f"rows sharded by nnz over {world} GPUs; X gathered over NVLink "
-                               f"({'copy-engine pulls from peer memory' if layer.spmm.exchange == 'peer' else 'NCCL send/recv steps'}), "
-                               f"overlapped with {len(shard.blocks)} column-block SpMMs per GPU",
+                               f"({EXCHANGE_NAMES.get(layer.spmm.exchange, layer.spmm.exchange)}), "
+                               f"overlapped with {n_blocks} column-block SpMMs per GPU",
                 "exchange": layer.spmm.exchange,
                 "cuda_graph": replay is not None,
                 "feature_slabs": layer.spmm.slabs,
@@ -584,7 +595,7 @@ def run(args):
             },
             # per step and GPU: two SpMM kernels (main + short-row queue) for every column block (or
             # feature band), and the Linear kernel
-            "gpu_launches": args.steps * world * ((layer.spmm.slabs or len(shard.blocks)) * 2 + 1),
+            "gpu_launches": args.steps * world * ((layer.spmm.slabs or n_blocks) * 2 + 1 + 1),  # + the weight split
             "clocks": clocks.summary(),
         }
         if not multi:

@@ -149,6 +149,14 @@ int asg_csr_row_softmax(const int64_t* crow, const float* scores, float* probs, 
  * pass with a running maximum and running sum per row, so scores and probabilities never reach
  * memory.  Rows without edges produce zeros.  scale = 1.0 reproduces the reference pipeline.
  */
+/*
+ * Workspace size with which asg_csr_attention also splits very long rows (4,096 edges or more) into
+ * 1,024-edge segments that different CTAs process and the last one merges: asg_workspace_bytes(n_rows)
+ * plus about 1 MB.  A workspace of only asg_workspace_bytes(n_rows) still works; such rows then stay
+ * with one CTA each.
+ */
+size_t asg_attention_workspace_bytes(int64_t n_rows);
+
 int asg_csr_attention(const int64_t* crow, const int64_t* col, const float* q, const float* k,
                       const float* v, float* out, int64_t n_rows, int64_t nnz, int64_t f,
                       float scale, int warps_per_block, int64_t hub_threshold, unsigned flags,
@@ -227,6 +235,16 @@ int asg_linear_bias_umma(const float* x, const float* weight, const float* bias,
  */
 int asg_copy_2d(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
                 size_t height, void* stream);
+
+/*
+ * Stores `bytes` bytes of src into each of destinations[0 .. n_destinations) (host array of device
+ * pointers, at most 7; peer-mapped memory of other GPUs is what it is meant for) from n_ctas CTAs
+ * (<= 0: 32) with plain 128-bit stores, reading src once.  src and every destination 16-byte aligned,
+ * bytes a multiple of 16.  The sharded path's SM-driven alternative to pulling shards with the copy
+ * engines.  No counterpart in the reference (single-GPU).
+ */
+int asg_push_to_peers(const void* src, void* const* destinations, int n_destinations, size_t bytes, int n_ctas,
+                      void* stream);
 
 /*
  * Status word written by kernels whose bounded waits gave up (0 = none).  The word lives in the

@@ -100,7 +100,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, overlap: bool, out_dir: str, groups=None):
+def _worker(rank: int, world: int, port: int, overlap: bool, out_dir: str, groups=None, exchange=None, chunks=2):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -111,8 +111,8 @@ def _worker(rank: int, world: int, port: int, overlap: bool, out_dir: str, group
         bounds = asg_dist.partition_rows(crow, world)
         shard = asg_dist.shard_csr(crow, col, val, rank, world, bounds, groups=groups)
         torch.manual_seed(0)
-        layer = asg_dist.ShardedAutoSAGEConv(shard, 24, 8)
-        assert layer.spmm.exchange == "nccl"  # CPU ranks use grouped send/recv
+        layer = asg_dist.ShardedAutoSAGEConv(shard, 24, 8, exchange=exchange, chunks=chunks)
+        assert layer.spmm.exchange == (exchange or "nccl")  # CPU ranks default to grouped send/recv
         layer.spmm.x_full.fill_(float("nan"))  # anything not received stays NaN and poisons the result
         with torch.no_grad():
             out = layer(x[shard.row_begin:shard.row_end], overlap=overlap)
@@ -125,9 +125,11 @@ def _worker(rank: int, world: int, port: int, overlap: bool, out_dir: str, group
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,overlap,groups", [(2, True, None), (2, False, None), (3, True, None), (3, True, 2)])
-def test_sharded_conv_on_gloo_ranks(tmp_path, world, overlap, groups):
-    mp.spawn(_worker, args=(world, _free_port(), overlap, str(tmp_path), groups), nprocs=world, join=True)
+@pytest.mark.parametrize("world,overlap,groups,exchange,chunks", [
+    (2, True, None, None, 2), (2, False, None, None, 2), (3, True, None, None, 2), (3, True, 2, None, 2),
+    (2, True, None, "allgather", 1), (3, True, None, "allgather", 3)])
+def test_sharded_conv_on_gloo_ranks(tmp_path, world, overlap, groups, exchange, chunks):
+    mp.spawn(_worker, args=(world, _free_port(), overlap, str(tmp_path), groups, exchange, chunks), nprocs=world, join=True)
     crow, col = random_csr(400, 9, seed=21, hubs={7: 900, 350: 300})
     val = weights(col.numel(), 4)
     x = dense(400, 24, 5)
@@ -208,3 +210,29 @@ def _failing_worker(rank: int, world: int, port: int, out_dir: str):
 def test_a_departed_rank_surfaces_as_an_error_on_the_host(tmp_path):
     mp.spawn(_failing_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     assert (tmp_path / "rank0.txt").read_text().startswith("error:")
+
+
+def test_chunked_layout_places_every_row_once():
+    """GatherLayout: positions are a bijection onto distinct buffer rows, own pieces are contiguous and
+    chunk c of every owner is one contiguous slice (what one all-gather fills)."""
+    bounds = torch.tensor([0, 5, 12, 12, 20])
+    for chunks in (1, 2, 3, 7):
+        layout = asg_dist.GatherLayout(bounds, chunks)
+        rows = torch.arange(20)
+        position = layout.position(rows)
+        assert position.unique().numel() == 20 and int(position.max()) < layout.rows_total
+        span = layout.world * layout.chunk_rows
+        assert torch.equal(torch.div(position, span, rounding_mode="floor"), layout.chunk_of(rows))
+        for rank in range(4):
+            covered = 0
+            for first, count, where in layout.local_pieces(rank):
+                mine = torch.arange(int(bounds[rank]) + first, int(bounds[rank]) + first + count)
+                assert torch.equal(layout.position(mine), torch.arange(where, where + count))
+                covered += count
+            assert covered == int(bounds[rank + 1] - bounds[rank])
+        buffer = torch.arange(layout.rows_total)
+        for c in range(layout.chunks):
+            whole = layout.chunk_view(buffer, c)
+            for rank in range(4):
+                own = layout.own_view(buffer, c, rank)
+                assert own.numel() == layout.chunk_rows and int(own[0]) == int(whole[rank * layout.chunk_rows])

@@ -41,7 +41,10 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
                                      ("peer_blocks_2streams", dict(exchange="peer", copy_streams=2), 1),
                                      ("peer_slabs2", dict(exchange="peer", slabs=2), 1),
                                      ("peer_slabs4", dict(exchange="peer", slabs=4, copy_streams=2), 1),
-                                     ("nccl_blocks", dict(exchange="nccl"), None)):
+                                     ("nccl_blocks", dict(exchange="nccl"), None),
+                                     ("allgather_1chunk", dict(exchange="allgather", chunks=1), None),
+                                     ("allgather_3chunks", dict(exchange="allgather", chunks=3), None),
+                                     ("push_2chunks", dict(exchange="push", chunks=2, push_ctas=8), None)):
             shard = asg_dist.shard_csr(crow, col, val, rank, world, bounds, device=device, groups=groups)
             torch.manual_seed(0)
             layer = asg_dist.ShardedAutoSAGEConv(shard, 128, 16, feature_tile=64, warps=4, threshold=1024,

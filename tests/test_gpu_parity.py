@@ -282,6 +282,31 @@ def test_fused_attention_matches_three_pass_oracle(lib, orc, features, scale):
         assert_close(orc, out, exact, crow)
 
 
+@pytest.mark.parametrize("features", [32, 64, 128, 256, 512])
+def test_fused_attention_splits_mega_rows_and_packs_short_rows(lib, orc, features):
+    """Rows of 4,096 edges or more are cut into segments that different CTAs process and merge (with the
+    larger workspace; one CTA per row with the small one); rows of fewer than 32 edges - every degree
+    from 0 to 31, so every lane-group fill of the packed short-row kernel - share warps."""
+    rows = 700
+    counts = torch.arange(rows) % 32                      # all short degrees, including empty rows
+    counts[3], counts[250], counts[699], counts[40] = 9000, 4096, 5000, 4095
+    crow, col = csr_from_counts(counts, rows, seed=features)
+    q, k, v = dense(rows, features, 31), dense(rows, features, 32), dense(rows, features, 33)
+    scale = float(features) ** -0.5
+    exact = orc.attention(to_np(crow), to_np(col), to_np(q), to_np(k), to_np(v), scale)
+    sizes = (lib.workspace_bytes(rows) + lib.attention_extra_bytes(rows), lib.workspace_bytes(rows))
+    assert sizes[0] > sizes[1]
+    for size in sizes:
+        for warps, threshold in ((8, 512), (4, 2048), (2, 100000)):
+            out = torch.full((rows, features), float("nan"), device="cuda")
+            ws = torch.empty(size, dtype=torch.uint8, device="cuda")
+            for _ in range(2):                            # twice: the completion counters are reset per call
+                lib.attention(crow.cuda(), col.cuda(), q.cuda(), k.cuda(), v.cuda(), out, scale=scale, warps=warps,
+                              threshold=threshold, flags=0, workspace=ws)
+            torch.cuda.synchronize()
+            assert_close(orc, out, exact, crow)
+
+
 def test_fused_attention_rejects_wide_rows(lib):
     crow, col = random_csr(8, 2, seed=1)
     t = torch.zeros(8, 516, device="cuda")
