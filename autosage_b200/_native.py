@@ -62,6 +62,7 @@ SIGNATURES = {
     "asg_workspace_status": (_INT, [_P, _P, _P]),
     "asg_spmm_csr_split_noalloc": (_INT, [_P, _P, _P, _P, _P, _I64, _I64, _I64, _INT, _INT, _I64, _P]),
     "asg_static_max_rows": (_I64, []),
+    "asg_static_status": (_INT, [_P, _P, _P]),
 }
 
 _LIB: Optional[ctypes.CDLL] = None

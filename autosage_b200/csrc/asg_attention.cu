@@ -485,14 +485,16 @@ __global__ void __launch_bounds__(512) attention_short_kernel(const AttentionArg
         const int mine = r0 + sub;                      // this group's row of the batch (may be past the end)
         const int src = mine < 32 ? mine : 31;
         const int row = __shfl_sync(kFull, row_l, src);
-        const int cnt = mine < n_here ? __shfl_sync(kFull, d_l, src) : 0;
+        const int cnt_any = __shfl_sync(kFull, d_l, src);  // every lane takes part in the shuffle
+        const int cnt = mine < n_here ? cnt_any : 0;
         int c_cur[CREG];
 #pragma unroll
         for (int k = 0; k < CREG; ++k) c_cur[k] = c_next[k];
         if (r0 + RPW < n_here) {  // warp-uniform
           const int ahead = r0 + RPW + sub < 32 ? r0 + RPW + sub : 31;
           const long long s1 = __shfl_sync(kFull, s_l, ahead);
-          const int d1 = r0 + RPW + sub < n_here ? __shfl_sync(kFull, d_l, ahead) : 0;
+          const int d1_any = __shfl_sync(kFull, d_l, ahead);
+          const int d1 = r0 + RPW + sub < n_here ? d1_any : 0;
 #pragma unroll
           for (int k = 0; k < CREG; ++k)
             c_next[k] = (l + k * G < d1) ? static_cast<int>(ld_index(a.col + s1 + l + k * G, pol_stream)) : 0;

@@ -106,11 +106,18 @@ __device__ __forceinline__ void spmm_short_rows(const SpmmArgs& a, int n_hub, in
           }
         }
         if (cnt == 0 && a.accumulate) continue;  // y += 0
+        // Accumulating (column blocks of the sharded path): the lanes that will store start from the
+        // row's current output, fetched before the gathers so that its latency hides behind them.
         float acc[NV][VW];
 #pragma unroll
-        for (int v = 0; v < NV; ++v)
+        for (int v = 0; v < NV; ++v) {
+          if (a.accumulate && sub == 0 && fvalid[v]) {
+            VecIO<VW>::load_plain(acc[v], a.y + static_cast<size_t>(row) * f + foff[v]);
+          } else {
 #pragma unroll
-          for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
+            for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
+          }
+        }
         for (int j = 0; j < cnt; j += BU) {
           float xv[U][NV][VW];
           float wu[U];
@@ -149,16 +156,7 @@ __device__ __forceinline__ void spmm_short_rows(const SpmmArgs& a, int n_hub, in
         if (sub == 0) {
 #pragma unroll
           for (int v = 0; v < NV; ++v) {
-            if (fvalid[v]) {
-              float* dst = a.y + static_cast<size_t>(row) * f + foff[v];
-              if (a.accumulate) {
-                float old[VW];
-                VecIO<VW>::load_plain(old, dst);
-#pragma unroll
-                for (int i = 0; i < VW; ++i) acc[v][i] += old[i];
-              }
-              VecIO<VW>::store(dst, acc[v]);
-            }
+            if (fvalid[v]) VecIO<VW>::store(a.y + static_cast<size_t>(row) * f + foff[v], acc[v]);
           }
         }
       }
@@ -398,17 +396,23 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
       const long long s = a.crow[row];
       const long long e = a.crow[row + 1];
 
-      float acc[NV][VW];
-#pragma unroll
-      for (int v = 0; v < NV; ++v)
-#pragma unroll
-        for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
       bool fvalid[NV];
       int foff[NV];
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
         foff[v] = fbase + VW * (l + G * v);
         fvalid[v] = foff[v] < f;
+      }
+      // accumulating: the storing lanes start from the row's current output (fetched under the gathers)
+      float acc[NV][VW];
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        if (a.accumulate && sub == 0 && fvalid[v]) {
+          VecIO<VW>::load_plain(acc[v], a.y + static_cast<size_t>(row) * f + foff[v]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
+        }
       }
 
       const bool tile_full = fbase + FT <= f;
@@ -491,16 +495,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
       if (sub == 0) {
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-          if (fvalid[v]) {
-            float* dst = a.y + static_cast<size_t>(row) * f + foff[v];
-            if (a.accumulate) {
-              float old[VW];
-              VecIO<VW>::load_plain(old, dst);
-#pragma unroll
-              for (int i = 0; i < VW; ++i) acc[v][i] += old[i];
-            }
-            VecIO<VW>::store(dst, acc[v]);
-          }
+          if (fvalid[v]) VecIO<VW>::store(a.y + static_cast<size_t>(row) * f + foff[v], acc[v]);
         }
       }
     }

@@ -20,7 +20,11 @@ constexpr int64_t kStaticMaxRows = 1 << 20;  // 1,048,576 rows
 // 256 B header + 4 B per row + counting-sort histogram (48 buckets x 1025 blocks x 4 B).
 constexpr size_t kStaticBytes = 256 + size_t(4) * kStaticMaxRows + 256 + size_t(4) * kBuckets * (kStaticMaxRows / kPlanBlock + 1) + 256;
 
-// One copy per GPU that loads the library (about 4.4 MB each), alive until the process exits.
+// One copy per GPU that loads the library (about 4.4 MB each), alive until the process exits.  With
+// the CUDA runtime's default lazy module loading the copy - and the kernels' code - is placed on a GPU
+// the first time this file's code touches that GPU, i.e. during the first asg_spmm_csr_split_noalloc
+// call there: that first call makes the driver allocate device memory and may synchronise the device,
+// so it belongs in the host's start-up phase, before its allocator is frozen and before any capture.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 
 // In host code `g_static_scratch` is only a handle for the runtime, not a device address, so the
@@ -68,6 +72,16 @@ int asg_spmm_csr_split_noalloc(const int64_t* crow, const int64_t* col, const fl
   // status word and the work counters left behind by the previous call.
   return asg_spmm_csr_split(crow, col, val, x, y, n_rows, nnz, f, feature_tile, warps_per_block, hub_threshold,
                             scratch, kStaticBytes, stream);
+}
+
+int asg_static_status(const void* device_pointer, int32_t* host_status, void* stream) {
+  using namespace asg;
+  ASG_REQUIRE(host_status != nullptr, ASG_EINVAL, "host_status must not be null");
+  void* scratch = nullptr;
+  DeviceGuard guard(device_pointer);  // null: the current device
+  ASG_CUDA(guard.status);
+  if (int rc = static_scratch(guard.target, &scratch)) return rc;
+  return asg_workspace_status(scratch, host_status, stream);
 }
 
 }  // extern "C"

@@ -266,7 +266,11 @@ int asg_workspace_status(const void* workspace, int32_t* host_status, void* stre
  *   - n_rows may be at most asg_static_max_rows() (1,048,576); larger graphs are rejected with
  *     ASG_ERANGE and a message naming the limit.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress,
- *     with that device current); make that first call before starting any stream capture.
+ *     with that device current); make that first call before starting any stream capture.  It is
+ *     also the moment at which the CUDA runtime (lazy module loading, its default) places the
+ *     library's code and this array on that GPU: the driver allocates device memory then and may
+ *     synchronise the device.  Make the first call per GPU - a one-row SpMM will do - while the
+ *     host is still starting up; every later call allocates nothing.
  *   - All calls on a device share the one array and each call rebuilds its contents from scratch,
  *     so nothing needs clearing between calls - but two calls that overlap on the GPU (different
  *     streams, or different host threads) race on it.  Issue them on one stream, or serialise them.
@@ -279,6 +283,14 @@ int asg_spmm_csr_split_noalloc(const int64_t* crow, const int64_t* col, const fl
 
 /* Largest n_rows asg_spmm_csr_split_noalloc accepts. */
 int64_t asg_static_max_rows(void);
+
+/*
+ * asg_workspace_status for the built-in scratch of asg_spmm_csr_split_noalloc: reads the status word of
+ * the array on the GPU that owns device_pointer (null: the current GPU) into *host_status,
+ * asynchronously on the given stream.  Non-zero: a bounded wait inside the last call's kernel gave up
+ * and its output is invalid.  No counterpart in the reference.
+ */
+int asg_static_status(const void* device_pointer, int32_t* host_status, void* stream);
 
 #ifdef __cplusplus
 }

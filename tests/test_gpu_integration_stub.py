@@ -83,9 +83,13 @@ def _stub_source() -> str:
     return stubs[0]
 
 
-def test_integration_stub_runs_the_reference_cuda_cases(native_library, tmp_path):
+def test_integration_stub_runs_the_reference_cuda_cases(tmp_path):
+    from autosage_b200 import build as builder
+
+    native_library = builder.library_path()   # the prebuilt file: a GPU box does not recompile
+    assert native_library.is_file(), "libautosage_b200.so has not been built"
     (tmp_path / "_b200.py").write_text(_stub_source(), encoding="utf-8")
     script = tmp_path / "drive_stub.py"
     script.write_text(textwrap.dedent(DRIVER.format(stub_dir=str(tmp_path), library=str(native_library))), encoding="utf-8")
-    done = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
+    done = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=240, cwd=str(tmp_path))
     assert done.returncode == 0 and "STUB-OK" in done.stdout, done.stdout[-2000:] + done.stderr[-4000:]

@@ -61,6 +61,13 @@ def test_noalloc_spmm_matches_the_regular_entry_point_twice():
                                                          threshold, stream))
             torch.cuda.synchronize()
             assert _within(actual, expected, crow)
+            # the status word of the built-in scratch is readable without knowing its address
+            import ctypes
+
+            status = ctypes.c_int32(-1)
+            _native.check(lib.asg_static_status(x.data_ptr(), ctypes.byref(status), stream))
+            torch.cuda.synchronize()
+            assert status.value == 0
 
         # and both agree with the CPU oracle
         from oracle import oracle
