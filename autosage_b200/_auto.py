@@ -44,6 +44,8 @@ from .ops import (DEFAULT_HUB_THRESHOLD, DEFAULT_TILE, DEFAULT_WARPS, SDDMM_HUB_
                   _normalize_csr, load_native, native_op, spmm_csr)
 
 AUTOTUNE_SCHEMA_VERSION = 3
+# (warps per CTA, hub threshold) the fused attention kernel is probed with first: the best of the B200 sweeps
+ATTENTION_DEFAULT = (4, 1024)
 _INF = float("inf")
 
 
@@ -895,7 +897,7 @@ def csr_attention_forward(crow, col, query, key, value, *, guardrail: float = 0.
         return three_pass, "sddmm+softmax+spmm"
 
     forced = config.warps_per_block is not None or config.hub_threshold is not None
-    pairs = _with_library_default(_warp_threshold_pairs(crow, query.size(1), config), (8, 512), forced)
+    pairs = _with_library_default(_warp_threshold_pairs(crow, query.size(1), config), ATTENTION_DEFAULT, forced)
     runs = []
     for warps, threshold in pairs:
         runs.append(([warps, threshold],
@@ -903,7 +905,7 @@ def csr_attention_forward(crow, col, query, key, value, *, guardrail: float = 0.
     result = _probe_and_choose(
         operation="attention", label="attention", config=config, device=device, graph=graph, cache=cache,
         sample_ms=sample_ms, sample=sample, make_baseline=make_baseline, candidates=runs, fallback=None, verbose=verbose,
-        preferred=(8, 512))
+        preferred=ATTENTION_DEFAULT)
     return finish(result, False)
 
 

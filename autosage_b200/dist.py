@@ -711,7 +711,7 @@ class ShardedAttention:
     """softmax_row(scale * Q K^T on the shard's CSR pattern) V for the shard's rows.  Q is row-local;
     K and V are gathered like X; the fused one-pass kernel then runs over the local rows."""
 
-    def __init__(self, shard: RowShard, features: int, *, group=None, warps: int = 8, threshold: int = 512,
+    def __init__(self, shard: RowShard, features: int, *, group=None, warps: int = 4, threshold: int = 1024,
                  exchange: Optional[str] = None) -> None:
         if features > 512:
             raise ValueError("the fused attention kernel takes at most 512 features")

@@ -122,7 +122,7 @@ def _single_gpu_extras(args, bench, shard, layer, algorithmic, n, nnz, f, out_f,
             # the CPU baselines of SDDMM and attention are timed once, on the F = 128 runs
             sub.no_cpu_baseline = args.no_cpu_baseline or not (label in ("c3_sddmm", "c4_attention"))
             sub.steps, sub.warmup = min(args.steps, 10), 3
-            sub.warps, sub.hub_threshold = {"c3_sddmm": (8, 8192), "c4_attention": (8, 512)}.get(workload, (4, 1024))
+            sub.warps, sub.hub_threshold = {"c3_sddmm": (8, 8192), "c4_attention": (4, 1024)}.get(workload, (4, 1024))
             torch.cuda.empty_cache()
             try:
                 got = bench.run_ours_single(sub)
