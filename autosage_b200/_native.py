@@ -23,6 +23,7 @@ FLAG_NO_VEC4 = 2
 FLAG_PLAN_READY = 4
 FLAG_NO_BULK_STAGE = 8
 FLAG_NO_TILE_PASSES = 16
+FLAG_PACK_SHORT_ROWS = 32
 
 _P = ctypes.c_void_p
 _I64 = ctypes.c_int64
@@ -208,6 +209,12 @@ def _plan_was_built(workspace: torch.Tensor) -> None:
     entry = _UNBUILT.pop(workspace.data_ptr(), None) if _UNBUILT else None
     if entry is not None:
         entry[3] = True
+    if os.getenv("AUTOSAGE_CHECK_STATUS") == "1" and not _capturing():
+        # debugging aid (synchronises): a kernel whose bounded wait gave up leaves a status word in
+        # the workspace header and returns with rows unwritten; turn that into an error here
+        status = workspace_status(workspace)
+        if status != 0:
+            raise RuntimeError(f"a kernel gave up a bounded wait (status {status}); its output is incomplete")
 
 
 def clear_plan_cache() -> None:

@@ -34,6 +34,7 @@ struct SpmmArgs {
   int tile_begin;   // index of the first of them (0 unless a feature range was requested)
   int accumulate;
   int bulk_stage;
+  int pack_short;  // queue 2 in the packed form (one row per lane group)
 };
 
 constexpr int kChunkPerWarp = 128;  // staged edges per warp and stage in the hub path
@@ -154,6 +155,155 @@ __device__ __forceinline__ void spmm_short_rows(const SpmmArgs& a, int n_hub, in
 #pragma unroll
             for (int i = 0; i < VW; ++i) acc[v][i] += __shfl_xor_sync(kFull, acc[v][i], o);
         if (sub == 0) {
+#pragma unroll
+          for (int v = 0; v < NV; ++v) {
+            if (fvalid[v]) VecIO<VW>::store(a.y + static_cast<size_t>(row) * f + foff[v], acc[v]);
+          }
+        }
+      }
+    }
+  }
+}
+
+// Queue 2, packed form (ASG_FLAG_PACK_SHORT_ROWS; the column blocks of the sharded path, whose rows hold a
+// quarter or an eighth of their edges): the warp still reads ids and pointers of 32 rows at once, but
+// walks them 32/G rows at a time - every group of G lanes, the lanes that together hold one feature tile
+// of a row, owns a row of its own, reads that row's columns (and weights) itself, gathers one X row per
+// step with U steps in flight and stores its own output tile, so nothing is reduced across groups.  A
+// 3-edge row costs the shared form two half-empty gather instructions, a cross-group reduction and a
+// store by half the lanes; two such rows share three instructions here.  On whole rows (a dozen edges,
+// degrees inside a 32-row grab differing by up to 2x) the shared form is faster: paired rows wait for
+// the longer of the two (measured: +10 % on the short-row kernel of the 2.4 M-row graph), so it stays the
+// default.
+template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL>
+__device__ __forceinline__ void spmm_short_rows_packed(const SpmmArgs& a, int n_hub, int n_medium, int n_short) {
+  constexpr int U = U_REQUESTED < 4 ? U_REQUESTED : 4;  // X rows in flight per lane group
+  constexpr int FT = VW * G * NV;
+  constexpr int RPW = 32 / G;                      // rows a warp processes side by side
+  constexpr int CREG = (kShortDegree + G - 1) / G;  // column registers per lane: G columns each
+  const int lane = threadIdx.x & 31;
+  const int l = lane % G;
+  const int sub = lane / G;
+  const int f = a.f;
+  const uint64_t pol_keep = policy_evict_last();
+  const uint64_t pol_stream = policy_evict_first();
+  if (n_short > 0) {
+    const int* shorts = a.order + n_hub + n_medium;
+    const int n_batches = (n_short + 31) / 32;
+    const long long total = static_cast<long long>(n_batches) * a.n_tiles;
+    for (;;) {
+      const unsigned long long it = warp_next(&a.header->counter[2]);
+      if (it >= static_cast<unsigned long long>(total)) break;
+      const int tile = static_cast<int>(it / n_batches);
+      const int first = static_cast<int>(it - static_cast<unsigned long long>(tile) * n_batches) * 32;
+      const int n_here = n_short - first < 32 ? n_short - first : 32;
+      const int fbase = (a.tile_begin + tile) * FT;
+      int row_l = 0;
+      long long s_l = 0;
+      int d_l = 0;
+      if (lane < n_here) {
+        row_l = shorts[first + lane];
+        s_l = a.crow[row_l];
+        d_l = static_cast<int>(a.crow[row_l + 1] - s_l);
+      }
+      bool fvalid[NV];
+      int foff[NV];
+#pragma unroll
+      for (int v = 0; v < NV; ++v) {
+        foff[v] = fbase + VW * (l + G * v);
+        fvalid[v] = foff[v] < f;
+      }
+      // columns / weights of the first rows: lane l of a group holds entries l, l + G, ... of its row
+      int c_next[CREG];
+      float w_next[CREG];
+      {
+        const long long s0 = __shfl_sync(kFull, s_l, sub);
+        const int d0 = __shfl_sync(kFull, d_l, sub);
+#pragma unroll
+        for (int k = 0; k < CREG; ++k) {
+          const bool has = l + k * G < d0;
+          c_next[k] = has ? static_cast<int>(ld_index(a.col + s0 + l + k * G, pol_stream)) : 0;
+          w_next[k] = (HAS_VAL && has) ? ld_weight(a.val + s0 + l + k * G, pol_stream) : 0.f;
+        }
+      }
+      for (int r0 = 0; r0 < n_here; r0 += RPW) {
+        const int mine = r0 + sub;  // this group's row of the batch (may lie past its end)
+        const int src = mine < 32 ? mine : 31;
+        const int row = __shfl_sync(kFull, row_l, src);
+        const int cnt_any = __shfl_sync(kFull, d_l, src);  // every lane takes part in the shuffles
+        const int cnt = mine < n_here ? cnt_any : 0;
+        int c_cur[CREG];
+        float w_cur[CREG];
+#pragma unroll
+        for (int k = 0; k < CREG; ++k) {
+          c_cur[k] = c_next[k];
+          w_cur[k] = w_next[k];
+        }
+        if (r0 + RPW < n_here) {  // warp-uniform: the next rows' columns while these rows gather
+          const int ahead = r0 + RPW + sub < 32 ? r0 + RPW + sub : 31;
+          const long long s1 = __shfl_sync(kFull, s_l, ahead);
+          const int d1_any = __shfl_sync(kFull, d_l, ahead);
+          const int d1 = r0 + RPW + sub < n_here ? d1_any : 0;
+#pragma unroll
+          for (int k = 0; k < CREG; ++k) {
+            const bool has = l + k * G < d1;
+            c_next[k] = has ? static_cast<int>(ld_index(a.col + s1 + l + k * G, pol_stream)) : 0;
+            w_next[k] = (HAS_VAL && has) ? ld_weight(a.val + s1 + l + k * G, pol_stream) : 0.f;
+          }
+        }
+        // Accumulating (column blocks of the sharded path): start from the row's current output,
+        // fetched before the gathers so that its latency hides behind them.
+        const bool writes = mine < n_here && (cnt > 0 || !a.accumulate);
+        float acc[NV][VW];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+          if (a.accumulate && writes && fvalid[v]) {
+            VecIO<VW>::load_plain(acc[v], a.y + static_cast<size_t>(row) * f + foff[v]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
+          }
+        }
+        const int longest = __reduce_max_sync(kFull, cnt);
+        for (int j = 0; j < longest; j += U) {
+          float xv[U][NV][VW];
+          float wu[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int e = j + u;
+            int c = 0;
+            float w = 0.f;
+#pragma unroll
+            for (int k = 0; k < CREG; ++k) {
+              const int lane_of = sub * G + ((e - k * G) & (G - 1));
+              const int got_c = __shfl_sync(kFull, c_cur[k], lane_of);
+              const float got_w = HAS_VAL ? __shfl_sync(kFull, w_cur[k], lane_of) : 1.f;
+              if (e >= k * G && e < (k + 1) * G) {
+                c = got_c;
+                w = got_w;
+              }
+            }
+            const bool ok = e < cnt;
+            wu[u] = ok ? w : 0.f;
+            const float* xrow = a.x + static_cast<long long>(c) * f;
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+              if (ok && fvalid[v]) {
+                VecIO<VW>::load(xv[u][v], xrow + foff[v], pol_keep);
+              } else {
+#pragma unroll
+                for (int i = 0; i < VW; ++i) xv[u][v][i] = 0.f;
+              }
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+#pragma unroll
+              for (int i = 0; i < VW; ++i) acc[v][i] = fmaf(wu[u], xv[u][v][i], acc[v][i]);
+        }
+        if (writes) {
 #pragma unroll
           for (int v = 0; v < NV; ++v) {
             if (fvalid[v]) VecIO<VW>::store(a.y + static_cast<size_t>(row) * f + foff[v], acc[v]);
@@ -518,11 +668,14 @@ __global__ void __launch_bounds__(512, 1) spmm_kernel_deep(const SpmmArgs a) {
   spmm_body<VW, G, NV, U, HAS_VAL>(a);
 }
 
-template <int VW, int G, int NV, int U, bool HAS_VAL>
+template <int VW, int G, int NV, int U, bool HAS_VAL, bool PACKED>
 __global__ void __launch_bounds__(512) spmm_short_kernel(const SpmmArgs a) {
   const int n_hub = a.header->n_hub;
   const int n_short = a.header->n_short;
-  if (n_short > 0) spmm_short_rows<VW, G, NV, U, HAS_VAL>(a, n_hub, a.header->n_light - n_short, n_short);
+  if (n_short > 0) {
+    if (PACKED) spmm_short_rows_packed<VW, G, NV, U, HAS_VAL>(a, n_hub, a.header->n_light - n_short, n_short);
+    else spmm_short_rows<VW, G, NV, U, HAS_VAL>(a, n_hub, a.header->n_light - n_short, n_short);
+  }
   pdl_wait_for_primary();  // do not complete before the main kernel has
 }
 
@@ -548,7 +701,8 @@ static int launch_instance(const SpmmArgs& args, int warps, cudaStream_t stream,
   kernel<<<grid, threads, smem, stream>>>(args);
   ASG_CUDA(cudaGetLastError());
   // queue 2 (rows of fewer than 32 edges); leaves at once when the plan has none
-  auto short_kernel = spmm_short_kernel<VW, G, NV, U, HAS_VAL>;
+  auto short_kernel = args.pack_short ? spmm_short_kernel<VW, G, NV, U, HAS_VAL, true>
+                                       : spmm_short_kernel<VW, G, NV, U, HAS_VAL, false>;
   int short_per_sm = 0;
   ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&short_per_sm, short_kernel, threads, 0));
   if (short_per_sm < 1) short_per_sm = 1;
@@ -649,6 +803,7 @@ static int spmm_entry(const int64_t* crow, const int64_t* col, const float* val,
     args.n_tiles = static_cast<int>((feature_count + feature_tile - 1) / feature_tile);
   }
   args.accumulate = (flags & ASG_FLAG_ACCUMULATE) ? 1 : 0;
+  args.pack_short = (flags & ASG_FLAG_PACK_SHORT_ROWS) ? 1 : 0;
   args.bulk_stage = (!(flags & ASG_FLAG_NO_BULK_STAGE) && aligned_to(col, 16) && (val == nullptr || aligned_to(val, 16))) ? 1 : 0;
   return launch_spmm(args, vw, feature_tile, warps, stream, guard.target);
 }

@@ -57,6 +57,7 @@ class ColumnBlock:
     val: Optional[torch.Tensor]
     workspace: Optional[torch.Tensor] = None
     plan_ready: bool = False
+    pack_short: bool = False   # rows hold a fraction of their edges: run short rows one per lane group
 
 
 @dataclass
@@ -247,6 +248,8 @@ def _block_spmm(block: ColumnBlock, x_full: torch.Tensor, y: torch.Tensor, accum
             block.workspace = torch.empty(_native.workspace_bytes(y.size(0)), dtype=torch.uint8, device=y.device)
             block.plan_ready = False
         flags = (_native.FLAG_ACCUMULATE if accumulate else 0) | (_native.FLAG_PLAN_READY if block.plan_ready else 0)
+        if block.pack_short:
+            flags |= _native.FLAG_PACK_SHORT_ROWS
         _native.spmm(block.crow, block.col, block.val, x_full, y, feature_tile=feature_tile, warps=warps,
                      threshold=threshold, flags=flags, workspace=block.workspace)
         block.plan_ready = True
@@ -281,7 +284,7 @@ class ShardedSpmm:
     def __init__(self, shard: RowShard, features: int, *, group=None, dtype=torch.float32, feature_tile: int = 128,
                  warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
                  exchange: Optional[str] = None, copy_streams: int = 1, slabs: int = 0, chunks: int = 2,
-                 push_ctas: int = 32) -> None:
+                 push_ctas: int = 32, pack_short_rows: bool = True) -> None:
         self.shard = shard
         self.group = group
         self.features = features
@@ -316,6 +319,9 @@ class ShardedSpmm:
             self.exchange = "peer" if self.handle is not None else "nccl"
         if not shard.groups:
             shard.groups = [[k] for k in arrival_order(shard.rank, shard.world)]
+        # a row of a column block holds 1/P .. 1/groups of its edges: short rows one per lane group
+        for block in (self._chunk_blocks if self.layout is not None else shard.blocks):
+            block.pack_short = bool(pack_short_rows) and shard.world > 1
         # Feature-slab mode (peer exchange only): X is pulled in `slabs` bands of feature columns, band s
         # of every remote shard before band s+1, and each band is multiplied over the WHOLE local CSR
         # as soon as it is complete.  No column blocks, so rows keep their full degree and nothing is
@@ -751,12 +757,12 @@ class ShardedAutoSAGEConv(torch.nn.Module):
     def __init__(self, shard: RowShard, in_channels: int, out_channels: int, *, bias: bool = True, group=None,
                  feature_tile: int = 128, warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
                  exchange: Optional[str] = None, copy_streams: int = 1, slabs: int = 0, chunks: int = 2,
-                 push_ctas: int = 32) -> None:
+                 push_ctas: int = 32, pack_short_rows: bool = True) -> None:
         super().__init__()
         self.linear = torch.nn.Linear(in_channels, out_channels, bias=bias)
         self.spmm = ShardedSpmm(shard, in_channels, group=group, feature_tile=feature_tile, warps=warps,
                                 threshold=threshold, exchange=exchange, copy_streams=copy_streams, slabs=slabs,
-                                chunks=chunks, push_ctas=push_ctas)
+                                chunks=chunks, push_ctas=push_ctas, pack_short_rows=pack_short_rows)
 
     def capture(self, warmup: int = 2):
         """Captures one inference forward (features already in ``spmm.x_local``) into a CUDA graph and

@@ -53,6 +53,7 @@ extern "C" {
 #define ASG_FLAG_PLAN_READY 4u /* workspace already holds a plan for this crow/threshold */
 #define ASG_FLAG_NO_BULK_STAGE 8u /* hub rows: stage col/val with plain loads, not bulk copies */
 #define ASG_FLAG_NO_TILE_PASSES 16u /* SDDMM: never split the feature dimension into 64-wide passes */
+#define ASG_FLAG_PACK_SHORT_ROWS 32u /* SpMM: rows under 32 edges one per lane group (for very short rows) */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int asg_version(void);

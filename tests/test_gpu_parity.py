@@ -85,6 +85,27 @@ def test_spmm_feature_widths(lib, orc, features, weighted):
         assert_close(orc, y, exact, crow)
 
 
+@pytest.mark.parametrize("features", [3, 32, 64, 100, 128, 256, 512])
+@pytest.mark.parametrize("weighted", [False, True])
+def test_spmm_packed_short_rows(lib, orc, features, weighted):
+    """ASG_FLAG_PACK_SHORT_ROWS: rows under 32 edges one per lane group - every degree from 0 to 31 (and
+    so every lane-group fill), with and without accumulation into an existing output."""
+    rows = 520
+    counts = torch.arange(rows) % 32
+    counts[5], counts[300] = 700, 45
+    crow, col = csr_from_counts(counts, rows, seed=features)
+    x = dense(rows, features, seed=2)
+    val = weights(col.numel(), 3) if weighted else None
+    exact = orc.spmm(to_np(crow), to_np(col), to_np(val), to_np(x))
+    for tile in (64, 128):
+        y = run_spmm(lib, crow, col, val, x, tile=tile, warps=4, threshold=256, flags=lib.FLAG_PACK_SHORT_ROWS)
+        assert_close(orc, y, exact, crow)
+        start = dense(rows, features, seed=9).cuda()
+        y = run_spmm(lib, crow, col, val, x, tile=tile, warps=4, threshold=256,
+                     flags=lib.FLAG_PACK_SHORT_ROWS | lib.FLAG_ACCUMULATE, y=start.clone())
+        assert_close(orc, y, exact + start.double().cpu().numpy(), crow)
+
+
 @pytest.mark.parametrize("tile", [32, 64, 128, 256])
 @pytest.mark.parametrize("warps", [2, 4, 8, 16])
 def test_spmm_tile_and_warp_grid(lib, orc, tile, warps):
