@@ -284,7 +284,7 @@ class ShardedSpmm:
     def __init__(self, shard: RowShard, features: int, *, group=None, dtype=torch.float32, feature_tile: int = 128,
                  warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
                  exchange: Optional[str] = None, copy_streams: int = 1, slabs: int = 0, chunks: int = 2,
-                 push_ctas: int = 32, pack_short_rows: bool = True) -> None:
+                 push_ctas: int = 32, pack_short_rows: bool = False) -> None:
         self.shard = shard
         self.group = group
         self.features = features
@@ -319,7 +319,9 @@ class ShardedSpmm:
             self.exchange = "peer" if self.handle is not None else "nccl"
         if not shard.groups:
             shard.groups = [[k] for k in arrival_order(shard.rank, shard.world)]
-        # a row of a column block holds 1/P .. 1/groups of its edges: short rows one per lane group
+        # A row of a column block holds 1/P .. 1/groups of its edges; running such short rows one per
+        # lane group (ASG_FLAG_PACK_SHORT_ROWS) was measured on 4 GPUs and did not pay (2.92 ms per step
+        # against 2.87 ms): off unless asked for.
         for block in (self._chunk_blocks if self.layout is not None else shard.blocks):
             block.pack_short = bool(pack_short_rows) and shard.world > 1
         # Feature-slab mode (peer exchange only): X is pulled in `slabs` bands of feature columns, band s
@@ -757,7 +759,7 @@ class ShardedAutoSAGEConv(torch.nn.Module):
     def __init__(self, shard: RowShard, in_channels: int, out_channels: int, *, bias: bool = True, group=None,
                  feature_tile: int = 128, warps: int = DEFAULT_WARPS, threshold: int = DEFAULT_HUB_THRESHOLD,
                  exchange: Optional[str] = None, copy_streams: int = 1, slabs: int = 0, chunks: int = 2,
-                 push_ctas: int = 32, pack_short_rows: bool = True) -> None:
+                 push_ctas: int = 32, pack_short_rows: bool = False) -> None:
         super().__init__()
         self.linear = torch.nn.Linear(in_channels, out_channels, bias=bias)
         self.spmm = ShardedSpmm(shard, in_channels, group=group, feature_tile=feature_tile, warps=warps,

@@ -177,6 +177,13 @@ def _probe_costs(bench, args, device) -> dict:
             else:
                 def call():
                     return autosage_b200.spmm_csr_auto(w["crow"], w["col"], w["val"], w["x"])[1]
+            # one plain (unscheduled) call first: the process is then warm - kernels loaded, output-sized
+            # blocks in torch's caching allocator - as it is when a model schedules its first layer
+            if workload == "c4_attention":
+                autosage_b200.csr_attention_forward(w["crow"], w["col"], w["q"], w["k"], w["v"], scale=args.features ** -0.5,
+                                                    fused=False)
+            else:
+                autosage_b200.spmm_csr(w["crow"], w["col"], w["val"], w["x"])
             laps = []
             for _ in range(2):
                 torch.cuda.synchronize()
@@ -554,7 +561,7 @@ def run(args):
                                f"({EXCHANGE_NAMES.get(layer.spmm.exchange, layer.spmm.exchange)}), "
                                f"overlapped with {n_blocks} column-block SpMMs per GPU",
                 "exchange": layer.spmm.exchange,
-                "cuda_graph": replay is not None,
+                "cuda_graph": replay is not None,  # N = 1 launches eagerly (host_enqueue_ms_per_step says what that costs)
                 "feature_slabs": layer.spmm.slabs,
                 "kernel_parameters": {"feature_tile": args.tile, "warps_per_block": args.warps,
                                       "hub_threshold": args.hub_threshold},
@@ -582,6 +589,8 @@ def run(args):
                 "h2d_bytes_per_step": int(io_bytes[0].item()),
                 "d2h_bytes_per_step": int(io_bytes[1].item()),
                 "steps": e2e_steps,
+                "inputs": "the CSR stays on the device (the layer's graph, as a model keeps its weights); this rank's X shard "
+                          "comes in from pinned host memory and its output shard goes back, every step",
                 "mode": "streamed: the copy-out of step i overlaps the copy-in and compute of step i+1 "
                         "(second stream, two pinned output buffers); every step's input and output cross PCIe "
                         "inside the timed region",
