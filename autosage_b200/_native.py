@@ -24,6 +24,7 @@ FLAG_PLAN_READY = 4
 FLAG_NO_BULK_STAGE = 8
 FLAG_NO_TILE_PASSES = 16
 FLAG_PACK_SHORT_ROWS = 32
+FLAG_SELFTEST_STALL = 64
 
 _P = ctypes.c_void_p
 _I64 = ctypes.c_int64

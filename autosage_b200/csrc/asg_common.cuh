@@ -166,14 +166,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: polls until the phase completes or about one second of wall time has passed
-// (global nanosecond timer), then returns false so the caller can record an error and leave.
+// Bounded wait: polls until the phase completes or `limit_ns` of wall time has passed (global
+// nanosecond timer; one second unless the caller says otherwise), then returns false so the caller can
+// record an error and leave.
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity) {
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;  // one second of wall time
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity,
+                                                  unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long start = global_ns();
   for (;;) {
@@ -181,7 +184,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
     for (int i = 0; i < 64; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
-    if (global_ns() - start > 1000000000ull) return false;
+    if (global_ns() - start > limit_ns) return false;
   }
 }
 // global -> shared bulk copy; both addresses 16-byte aligned, bytes a multiple of 16.

@@ -35,6 +35,8 @@ struct SpmmArgs {
   int accumulate;
   int bulk_stage;
   int pack_short;  // queue 2 in the packed form (one row per lane group)
+  int selftest_stall;  // ASG_FLAG_SELFTEST_STALL: hub staging announces 16 bytes that never arrive
+  unsigned long long wait_limit_ns;
 };
 
 constexpr int kChunkPerWarp = 128;  // staged edges per warp and stage in the hub path
@@ -333,6 +335,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
 
   // shared memory carve-up
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);                       // 2 mbarriers
+  uint64_t* idle_bar = reinterpret_cast<uint64_t*>(smem + 32);              // self-test: nothing ever arrives here
   int* s_item = reinterpret_cast<int*>(smem + 16);                          // CTA-wide item id
   long long* s_col = reinterpret_cast<long long*>(smem + 128);              // [2][chunk]
   float* s_val = reinterpret_cast<float*>(smem + 128 + size_t(16) * chunk); // [2][chunk]
@@ -349,6 +352,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
     if (tid == 0) {
       mbar_init(&bars[0], 1);
       mbar_init(&bars[1], 1);
+      mbar_init(idle_bar, 1);
       mbar_fence_init();
     }
     unsigned seq = 0;  // chunks staged so far by this CTA: stage = seq & 1, parity = (seq >> 1) & 1
@@ -418,18 +422,23 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
 
       if (n_chunks > 0) stage_chunk(0, seq);
       __syncthreads();
-      // Every thread runs every iteration (the barriers below are CTA-wide); a thread whose
-      // bounded wait expired stops consuming and the CTA leaves together after the loop.
-      for (int k = 0; k < n_chunks; ++k) {
-        if (k + 1 < n_chunks) stage_chunk(k + 1, seq + 1);
+      // `alive` is the same in every thread at the head of an iteration: once any thread's bounded wait
+      // has run out, nothing more is staged (a barrier whose phase never completed must not be armed a
+      // second time) and the CTA leaves together after the loop.
+      int staged_ahead = 0;  // a chunk beyond the one being waited for is in flight
+      for (int k = 0; k < n_chunks && alive; ++k) {
+        staged_ahead = k + 1 < n_chunks ? 1 : 0;
+        if (staged_ahead) stage_chunk(k + 1, seq + 1);
         const int st = seq & 1;
-        if (a.bulk_stage && alive) {
-          if (!mbar_wait_bounded(&bars[st], (seq >> 1) & 1)) {
-            atomicCAS(&a.header->status, 0, kStatusBulkWaitExpired);
-            alive = false;
-          }
+        bool arrived = true;
+        if (a.bulk_stage) {
+          // self-test: wait on a barrier nobody arrives on (no copy targets it, so nothing is pending
+          // on it when the CTA leaves); the staging itself runs and completes as usual
+          uint64_t* awaited = a.selftest_stall ? idle_bar : &bars[st];
+          arrived = mbar_wait_bounded(awaited, a.selftest_stall ? 0u : ((seq >> 1) & 1), a.wait_limit_ns);
+          if (!arrived) atomicCAS(&a.header->status, 0, kStatusBulkWaitExpired);
         }
-        if (alive) {
+        if (arrived) {
           const long long g0 = a0 + static_cast<long long>(k) * chunk;
           const long long g1 = g0 + chunk < e ? g0 + chunk : e;
           const long long lo = g0 > s ? g0 : s;
@@ -492,15 +501,20 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
         }
         ++seq;
         // All warps have finished reading this stage (and the plain-store tail of the next stage
-        // is visible) before the stage is refilled.
+        // is visible) before the stage is refilled; the same barrier tells every thread whether
+        // some thread's wait ran out.
         if (a.bulk_stage) fence_proxy_async();
-        __syncthreads();
+        alive = __syncthreads_or(!arrived) == 0;
       }
-      // a bounded wait gave up in some thread: every thread leaves together, after one more
-      // bounded wait for the copies that may still be in flight into this CTA's shared memory
-      if (__syncthreads_or(!alive)) {
-        if (tid == 0 && a.bulk_stage && seq > 0) mbar_wait_bounded(&bars[(seq - 1) & 1], ((seq - 1) >> 1) & 1);
-        alive = false;
+      // a bounded wait gave up in some thread: every thread leaves together, after one more bounded
+      // wait for each copy that may still be in flight into this CTA's shared memory (the chunk that
+      // was being waited for and the one staged ahead of it)
+      if (!alive) {
+        if (tid == 0 && a.bulk_stage && seq > 0) {
+          mbar_wait_bounded(&bars[(seq - 1) & 1], ((seq - 1) >> 1) & 1, a.wait_limit_ns);
+          if (staged_ahead) mbar_wait_bounded(&bars[seq & 1], (seq >> 1) & 1, a.wait_limit_ns);
+        }
+        __syncthreads();
         break;
       }
 
@@ -804,6 +818,11 @@ static int spmm_entry(const int64_t* crow, const int64_t* col, const float* val,
   }
   args.accumulate = (flags & ASG_FLAG_ACCUMULATE) ? 1 : 0;
   args.pack_short = (flags & ASG_FLAG_PACK_SHORT_ROWS) ? 1 : 0;
+  // Self-test of the give-up path: the hub staging waits on a barrier on which nothing ever arrives, so
+  // the wait can only run out (after 20 ms instead of a second); the copies themselves complete normally
+  // on their own barriers, which the leaving CTA still waits for.
+  args.selftest_stall = (flags & ASG_FLAG_SELFTEST_STALL) ? 1 : 0;
+  args.wait_limit_ns = args.selftest_stall ? 20000000ull : kWaitLimitNs;
   args.bulk_stage = (!(flags & ASG_FLAG_NO_BULK_STAGE) && aligned_to(col, 16) && (val == nullptr || aligned_to(val, 16))) ? 1 : 0;
   return launch_spmm(args, vw, feature_tile, warps, stream, guard.target);
 }

@@ -54,6 +54,9 @@ extern "C" {
 #define ASG_FLAG_NO_BULK_STAGE 8u /* hub rows: stage col/val with plain loads, not bulk copies */
 #define ASG_FLAG_NO_TILE_PASSES 16u /* SDDMM: never split the feature dimension into 64-wide passes */
 #define ASG_FLAG_PACK_SHORT_ROWS 32u /* SpMM: rows under 32 edges one per lane group (for very short rows) */
+#define ASG_FLAG_SELFTEST_STALL 64u /* SpMM self-test: the hub staging waits on a barrier nobody arrives on, so
+                                       its bounded wait (20 ms here) gives up, the status word becomes 1 and the
+                                       kernel returns with the hub rows unwritten; nothing faults or hangs */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int asg_version(void);

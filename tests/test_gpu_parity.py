@@ -106,6 +106,35 @@ def test_spmm_packed_short_rows(lib, orc, features, weighted):
         assert_close(orc, y, exact + start.double().cpu().numpy(), crow)
 
 
+def test_bounded_wait_gives_up_and_reports(lib, orc, monkeypatch):
+    """The give-up path of the hub staging: with ASG_FLAG_SELFTEST_STALL every stage announces 16 bytes that
+    never arrive, so the wait runs out after its (shortened) limit; the kernel must return, leave status 1
+    in the workspace, still produce the light rows, and the next ordinary call on the same workspace must
+    be clean.  AUTOSAGE_CHECK_STATUS=1 turns the status into an exception."""
+    crow, col = random_csr(600, 6, seed=12, hubs={17: 3000, 400: 1500})
+    x = dense(600, 64, seed=4)
+    dev = torch.device("cuda")
+    crow_d, col_d, x_d = crow.to(dev), col.to(dev), x.to(dev)
+    ws = torch.empty(lib.workspace_bytes(600), dtype=torch.uint8, device=dev)
+    y = torch.full((600, 64), float("nan"), device=dev)
+    lib.spmm(crow_d, col_d, None, x_d, y, feature_tile=64, warps=4, threshold=1024, flags=lib.FLAG_SELFTEST_STALL,
+             workspace=ws)
+    torch.cuda.synchronize()
+    assert lib.workspace_status(ws) == 1
+    exact = orc.spmm(to_np(crow), to_np(col), None, to_np(x))
+    light = torch.ones(600, dtype=torch.bool)
+    light[[17, 400]] = False
+    assert np.abs(y.cpu().numpy()[light.numpy()] - exact[light.numpy()]).max() < 1e-3   # light rows were computed
+    assert bool(torch.isnan(y[17]).all()) and bool(torch.isnan(y[400]).all())             # hub rows were not
+    monkeypatch.setenv("AUTOSAGE_CHECK_STATUS", "1")
+    with pytest.raises(RuntimeError, match="gave up a bounded wait"):
+        lib.spmm(crow_d, col_d, None, x_d, y, feature_tile=64, warps=4, threshold=1024, flags=lib.FLAG_SELFTEST_STALL,
+                 workspace=ws)
+    monkeypatch.delenv("AUTOSAGE_CHECK_STATUS")
+    y = run_spmm(lib, crow, col, None, x, tile=64, warps=4, threshold=1024, ws=ws)      # asserts status == 0
+    assert_close(orc, y, exact, crow)
+
+
 @pytest.mark.parametrize("tile", [32, 64, 128, 256])
 @pytest.mark.parametrize("warps", [2, 4, 8, 16])
 def test_spmm_tile_and_warp_grid(lib, orc, tile, warps):
