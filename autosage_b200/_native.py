@@ -55,6 +55,7 @@ SIGNATURES = {
     "asg_csr_from_edges": (_INT, [_P, _P, _P, _I64, _I64, _P, _P, _P, _P, _P, _SZ, _P]),
     "asg_row_sample_workspace_bytes": (_SZ, [_I64]),
     "asg_csr_row_sample": (_INT, [_P, _P, _P, _P, _I64, _I64, _P, _P, _P, _P, _P, _SZ, _P]),
+    "asg_linear_available": (_INT, []),
     "asg_linear_bias": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "asg_linear_workspace_bytes": (_SZ, [_I64, _I64]),
     "asg_linear_supported": (_INT, [_I64, _I64]),

@@ -58,9 +58,10 @@ def apply_linear(linear: nn.Linear, aggregated: torch.Tensor) -> torch.Tensor:
             if (os.getenv("AUTOSAGE_LINEAR_KERNEL", "umma") == "umma"
                     and _native.linear_umma_supported(x.size(1), linear.out_features)):
                 _native.linear_bias_umma(x.detach(), weight, bias, out)   # the hand-written tcgen05 kernel
-            else:
+                return out
+            if _native.library().asg_linear_available():
                 _native.linear_bias(x.detach(), weight, bias, out)        # other sizes: the CUTLASS instantiation
-            return out
+                return out
         out = torch.mm(aggregated, linear.weight.t())
         if linear.bias is None:
             return out

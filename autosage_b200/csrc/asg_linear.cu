@@ -15,6 +15,15 @@
 // instantiation (tile 128x128x16, one SM per tile, per-column bias fusion) and the C entry are ours.
 #include "asg_common.cuh"
 
+#ifdef ASG_NO_CUTLASS
+// Built without a CUTLASS header tree: the entry point exists (the ABI stays complete) and says so.
+extern "C" int asg_linear_available(void) { return 0; }
+extern "C" int asg_linear_bias(const float*, const float*, const float*, float*, int64_t, int64_t, int64_t, void*) {
+  return asg::fail(ASG_EINVAL, "%s", "asg_linear_bias was built without CUTLASS; use asg_linear_bias_umma or a cuBLAS product");
+}
+#else
+extern "C" int asg_linear_available(void) { return 1; }
+
 #include "cute/tensor.hpp"
 #include "cutlass/cutlass.h"
 #include "cutlass/epilogue/collective/collective_builder.hpp"
@@ -124,3 +133,4 @@ extern "C" int asg_linear_bias(const float* x, const float* weight, const float*
   }
   return ASG_OK;
 }
+#endif  // ASG_NO_CUTLASS

@@ -39,9 +39,13 @@ def _native_build_ok(row_of_edge: torch.Tensor, num_nodes: int) -> bool:
         return False
     if row_of_edge.numel() >= 2 ** 31 or num_nodes >= 2 ** 31 or num_nodes < 1:
         return False
-    from ..ops import load_native
+    from ..ops import load_native, native_load_error
 
-    return bool(load_native())
+    if not load_native():
+        # no silent torch fallback on the GPU path: a CUDA call without the library is an error, as it
+        # is for the operators (AUTOSAGE_CSR_BUILD=torch selects the torch formulation explicitly)
+        raise RuntimeError(f"AutoSAGE CUDA extension is unavailable: {native_load_error()}")
+    return True
 
 
 def csr_with_order(edge_index: torch.Tensor, num_nodes: int, *, rows_by: str = "dst", want_order: bool = False,

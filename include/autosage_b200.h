@@ -216,6 +216,9 @@ int asg_csr_row_sample(const int64_t* crow, const int64_t* col, const float* val
  */
 int asg_linear_bias(const float* x, const float* weight, const float* bias, float* out, int64_t rows,
                     int64_t in_features, int64_t out_features, void* stream);
+/* 1 when asg_linear_bias is usable, 0 when the library was built without a CUTLASS header tree (the
+ * entry point then returns ASG_EINVAL; asg_linear_bias_umma is unaffected). */
+int asg_linear_available(void);
 
 /*
  * The same product as asg_linear_bias from the hand-written tcgen05 kernel (csrc/asg_linear_umma.cu):
