@@ -817,7 +817,7 @@ def _attention_unfused(crow, col, query, key, value, scale, guardrail, seed, ver
     return output, {"sddmm": sddmm_info, "spmm": spmm_info}
 
 
-def _run_fused_attention(crow, col, query, key, value, scale, warps, threshold) -> torch.Tensor:
+def _fused_attention_kernel(crow, col, query, key, value, scale, warps, threshold) -> torch.Tensor:
     out = torch.empty_like(query)  # one output row per CSR row (the probe's row sample is k x N)
     if out.numel() == 0:
         return out
@@ -827,6 +827,56 @@ def _run_fused_attention(crow, col, query, key, value, scale, warps, threshold) 
     return out
 
 
+class _FusedAttention(torch.autograd.Function):
+    """The fused kernel with a backward pass.  Forward: one pass, nothing per edge kept.  Backward
+    recomputes the probabilities with the library's own kernels instead of storing them:
+        S = scale * SDDMM(Q, K),  P = row_softmax(S),  DP = SDDMM(dOut, V),  D_r = <dOut_r, Out_r>
+        dS = P * (DP - D[row]) * scale
+        dQ = A(dS) K,   dK = A(dS)^T Q,   dV = A(P)^T dOut
+    (A(w) = the CSR pattern with edge weights w; the transposed products run over the memoised transposed
+    pattern, as the operators' own gradients do.)  The reference registers no gradient at all
+    (csrc/spmm_binding.cpp:72-75); its Python pipeline is differentiable only through torch's ops."""
+
+    @staticmethod
+    def forward(ctx, crow, col, query, key, value, scale, warps, threshold):
+        out = _fused_attention_kernel(crow, col, query, key, value, scale, warps, threshold)
+        ctx.save_for_backward(crow, col, query, key, value, out)
+        ctx.scale = 1.0 if scale is None else float(scale)
+        return out
+
+    @staticmethod
+    @torch.no_grad()
+    def backward(ctx, grad_out):
+        from .ops import _transposed_pattern
+
+        crow, col, query, key, value, out = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        scale = ctx.scale
+        ops = torch.ops.autosage
+        scores = ops.sddmm_csr(crow, col, query * scale if scale != 1.0 else query, key)
+        probs = _csr_row_softmax(crow, scores)
+        rows = _row_ids(crow)
+        row_dot = (grad_out * out).sum(dim=1)
+        grad_scores = probs * (ops.sddmm_csr(crow, col, grad_out, value) - row_dot.index_select(0, rows)) * scale
+        grad_q = grad_k = grad_v = None
+        need_q, need_k, need_v = ctx.needs_input_grad[2:5]
+        if need_q:
+            grad_q = ops.spmm_csr(crow, col, grad_scores, key)
+        if need_k or need_v:
+            crow_t, col_t, perm = _transposed_pattern(crow, col)
+            if need_k:
+                grad_k = ops.spmm_csr(crow_t, col_t, grad_scores[perm].contiguous(), query)
+            if need_v:
+                grad_v = ops.spmm_csr(crow_t, col_t, probs[perm].contiguous(), grad_out)
+        return None, None, grad_q, grad_k, grad_v, None, None, None
+
+
+def _run_fused_attention(crow, col, query, key, value, scale, warps, threshold) -> torch.Tensor:
+    if torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad):
+        return _FusedAttention.apply(crow, col, query, key, value, scale, warps, threshold)
+    return _fused_attention_kernel(crow, col, query, key, value, scale, warps, threshold)
+
+
 def csr_attention_forward(crow, col, query, key, value, *, guardrail: float = 0.95, seed: int = 0,
                           verbose: bool = False, scale: Optional[float] = None,
                           fused: Optional[bool] = None) -> tuple[torch.Tensor, dict[str, Any]]:
@@ -834,13 +884,13 @@ def csr_attention_forward(crow, col, query, key, value, *, guardrail: float = 0.
 
     ``scale=None`` is the reference behaviour (no scaling, ``_auto.py:762-780``).  On float32 CUDA
     inputs with at most 512 features the one-pass fused kernel is scheduled like the other
-    operators (probe on the induced sample against the three-pass pipeline, guardrail, cache under
+    operators (probe on the sample against the three-pass pipeline, guardrail, cache under
     operation "attention"); ``fused=False`` or AUTOSAGE_FUSED_ATTENTION=0 forces the reference's
-    three-pass composition.  The info dict keeps the reference's two keys and adds "attention".
+    three-pass composition.  The fused kernel is differentiable in query, key and value (its backward
+    recomputes the probabilities, see ``_FusedAttention``).  The info dict keeps the reference's two
+    keys and adds "attention".
     """
     use_fused = _fused_attention_enabled() if fused is None else bool(fused)
-    if torch.is_grad_enabled() and (query.requires_grad or key.requires_grad or value.requires_grad):
-        use_fused = False  # the fused kernel is forward-only; the three-pass composition is differentiable
     eligible = (query.is_cuda and query.dtype == torch.float32 and key.dtype == torch.float32
                 and value.dtype == torch.float32 and query.ndim == 2 and query.shape == key.shape == value.shape
                 and query.size(1) <= 512)

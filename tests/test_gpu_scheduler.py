@@ -252,17 +252,46 @@ def test_operators_are_differentiable(asg, isolated_cache):
     assert torch.allclose(got_q, q.grad, rtol=1e-4, atol=1e-3)
     assert torch.allclose(got_k, k.grad, rtol=1e-4, atol=1e-3)
 
-    # the layer trains: loss goes through AutoSAGEConv on the GPU, attention falls back to the
-    # differentiable three-pass composition when gradients are requested
+    # the layer trains: loss goes through AutoSAGEConv on the GPU
     layer = asg.AutoSAGEConv(48, 8, mode="native").cuda()
     edge_index = torch.stack((col_d, rows))
     layer(x, edge_index).square().mean().backward()
     assert layer.linear.weight.grad is not None and torch.isfinite(layer.linear.weight.grad).all()
-    qq = dense(n, 32, 9).cuda().requires_grad_()
-    out, info = asg.csr_attention_forward(crow_d, col_d, qq, k.detach(), dense(n, 32, 10).cuda(), scale=0.2)
-    assert set(info) == {"sddmm", "spmm"}
-    out.sum().backward()
-    assert qq.grad is not None and torch.isfinite(qq.grad).all()
+
+
+def test_fused_attention_backward_matches_the_three_pass_gradients(asg):
+    """The fused kernel's backward (probabilities recomputed with the library's kernels) against the
+    gradients torch's autograd takes through the reference formulation of the pipeline in float64:
+    gather-dot scores, scatter softmax, index_add aggregation."""
+    n, f, scale = 900, 64, 0.125
+    crow, col = random_csr(n, 7, seed=41, hubs={3: 1400, 500: 90})
+    dev = torch.device("cuda")
+    crow_d, col_d = crow.to(dev), col.to(dev)
+    rows = torch.repeat_interleave(torch.arange(n, device=dev), crow_d[1:] - crow_d[:-1])
+    base = [dense(n, f, seed).to(dev) for seed in (51, 52, 53)]
+    weight = dense(n, f, 54).to(dev)                      # d(loss)/d(out)
+
+    q, k, v = (t.clone().requires_grad_() for t in base)
+    out, info = asg.csr_attention_forward(crow_d, col_d, q, k, v, scale=scale, fused=True)
+    assert "attention" in info                            # the fused path ran although gradients are wanted
+    (out * weight).sum().backward()
+
+    q64, k64, v64 = (t.double().clone().requires_grad_() for t in base)
+    scores = (q64[rows] * k64[col_d]).sum(1) * scale
+    peak = torch.full((n,), -torch.inf, dtype=torch.float64, device=dev).scatter_reduce(0, rows, scores, "amax")
+    e = (scores - peak[rows]).exp()
+    p = e / torch.zeros(n, dtype=torch.float64, device=dev).index_add(0, rows, e)[rows]
+    out64 = torch.zeros(n, f, dtype=torch.float64, device=dev).index_add(0, rows, p[:, None] * v64[col_d])
+    (out64 * weight.double()).sum().backward()
+    assert torch.allclose(out.double(), out64, rtol=1e-4, atol=1e-5)
+    for got, want, name in ((q.grad, q64.grad, "dQ"), (k.grad, k64.grad, "dK"), (v.grad, v64.grad, "dV")):
+        scale_of = float(want.abs().max())
+        assert float((got.double() - want).abs().max()) <= 2e-4 * scale_of + 1e-6, name
+    # only one operand differentiable: the others' gradients are skipped, not wrong
+    q2 = base[0].clone().requires_grad_()
+    out2, _ = asg.csr_attention_forward(crow_d, col_d, q2, base[1], base[2], scale=scale, fused=True)
+    (out2 * weight).sum().backward()
+    assert torch.allclose(q2.grad, q.grad, rtol=1e-5, atol=1e-6)
 
 
 def test_operators_replay_inside_a_cuda_graph(asg, orc):
