@@ -74,6 +74,24 @@ def apply_linear(linear: nn.Linear, aggregated: torch.Tensor) -> torch.Tensor:
     return linear(aggregated)
 
 
+def _fused_forward_ok(linear: nn.Linear, x: torch.Tensor, weights: Optional[torch.Tensor]) -> bool:
+    """The one-kernel form of the layer (aggregation and Linear fused, ``AUTOSAGE_CONV_FUSED=1``): CUDA
+    float32, no gradient wanted, 64 or 128 input features, output features a multiple of 32 up to 256."""
+    if os.getenv("AUTOSAGE_CONV_FUSED", "0") != "1" or not x.is_cuda or x.dtype != torch.float32 or x.dim() != 2:
+        return False
+    tensors = [x, linear.weight, linear.bias] + ([] if weights is None else [weights])
+    if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in tensors):
+        return False
+    from . import _native
+    from .ops import load_native
+
+    if not load_native() or not _native.conv_fused_supported(x.size(1), linear.out_features):
+        return False
+    return (x.is_contiguous() and x.data_ptr() % 32 == 0 and linear.weight.dtype == torch.float32
+            and linear.weight.device == x.device and (linear.bias is None or linear.bias.dtype == torch.float32)
+            and (weights is None or weights.dtype == torch.float32) and x.size(0) < 2 ** 31 - 2048)
+
+
 class _CsrMemo:
     """Last (edge_index -> crow, col, edge permutation) conversion, valid while the same tensor object
     is passed again unmodified."""
@@ -118,6 +136,18 @@ class AutoSAGEConv(nn.Module):
                 raise ValueError("edge_weight and edge_index must be on the same device")
         crow, col, order = self._csr.get(edge_index, x.size(0), edge_weight is not None)
         weights = None if edge_weight is None else edge_weight.index_select(0, order)
+        if _fused_forward_ok(self.linear, x, weights):
+            # Opt-in: it measured slower than the two kernels below on the large benchmark graph (the
+            # gather inside the fused kernel runs with one CTA per SM), so it is not scheduled by default.
+            from . import _native
+
+            output = torch.empty(x.size(0), self.linear.out_features, dtype=torch.float32, device=x.device)
+            bias = None if self.linear.bias is None else self.linear.bias.detach().contiguous()
+            _native.conv_fused(crow, col, None if weights is None else weights.contiguous(), x,
+                               self.linear.weight.detach().contiguous(), bias, output)
+            info = {"operation": "conv_fused", "choice": "fused", "from_cache": False,
+                    "hub_threshold": _native.CONV_FUSED_HUB_THRESHOLD}
+            return (output, info) if return_info else output
         if self.mode == "auto":
             aggregated, info = spmm_csr_auto(crow, col, weights, x)
         else:

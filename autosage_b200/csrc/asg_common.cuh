@@ -101,6 +101,12 @@ int check_workspace(const void* workspace, size_t bytes, int64_t n_rows);
 int plan_build(const int64_t* crow, int64_t n_rows, int64_t hub_threshold, void* workspace,
                cudaStream_t stream);
 int reset_counters(void* workspace, cudaStream_t stream);
+// Hub rows (degree >= hub_threshold) only: the aggregated row of hub item i of the plan goes to
+// hub_y + i * f and hub_slot[row] = i (asg_spmm.cu).  Takes the flags of asg_spmm_csr_ex.
+int spmm_hub_rows_compact(const int64_t* crow, const int64_t* col, const float* val, const float* x, float* hub_y,
+                          int* hub_slot, int64_t n_rows, int64_t nnz, int64_t f, int feature_tile, int warps,
+                          int64_t hub_threshold, unsigned flags, void* workspace, size_t workspace_bytes,
+                          cudaStream_t stream);
 
 // status codes kernels may record in Header::status
 constexpr int kStatusBulkWaitExpired = 1;
@@ -160,6 +166,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking test of a phase (try_wait may suspend the thread for a while before it answers).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)

@@ -323,6 +323,13 @@ inline size_t packed_bytes(int64_t k, int64_t n) {
   return static_cast<size_t>(k / kBlockK) * kPieces * static_cast<size_t>(n) * kSwizzleRowBytes;
 }
 
+// Also called by the fused aggregation + Linear kernel (asg_conv_fused.cu), which reads the same image.
+int pack_weight_pieces(const float* weight, unsigned char* packed, int n, int k, cudaStream_t stream) {
+  pack_weight<<<(n * k + 255) / 256, 256, 0, stream>>>(weight, packed, n, k);
+  ASG_CUDA(cudaGetLastError());
+  return ASG_OK;
+}
+
 }  // namespace linear_umma
 }  // namespace asg
 
@@ -364,8 +371,7 @@ extern "C" int asg_linear_bias_umma(const float* x, const float* weight, const f
   unsigned char* packed = static_cast<unsigned char*>(workspace) + 256;
   ASG_CUDA(cudaMemsetAsync(&header->status, 0, sizeof(int), stream));
   const int n = static_cast<int>(out_features), k = static_cast<int>(in_features);
-  pack_weight<<<(n * k + 255) / 256, 256, 0, stream>>>(weight, packed, n, k);
-  ASG_CUDA(cudaGetLastError());
+  if (int rc = pack_weight_pieces(weight, packed, n, k, stream)) return rc;
 
   Args args;
   args.x = x;

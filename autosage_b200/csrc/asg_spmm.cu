@@ -37,6 +37,11 @@ struct SpmmArgs {
   int pack_short;  // queue 2 in the packed form (one row per lane group)
   int selftest_stall;  // ASG_FLAG_SELFTEST_STALL: hub staging announces 16 bytes that never arrive
   unsigned long long wait_limit_ns;
+  // Hub rows only, written compactly (the first pass of the fused aggregation + Linear kernel): the sum
+  // of hub item i goes to y + i * f instead of y + row * f, and hub_slot[row] = i tells the second pass
+  // where to find it.  Queues 1 and 2 are not touched.
+  int hubs_only;
+  int* hub_slot;
 };
 
 constexpr int kChunkPerWarp = 128;  // staged edges per warp and stage in the hub path
@@ -368,8 +373,10 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
       const int item = *s_item;
       if (item < 0) break;
       const int tile = item / n_hub;
-      const int row = a.order[item - tile * n_hub];
+      const int hub_index = item - tile * n_hub;
+      const int row = a.order[hub_index];
       const int fbase = (a.tile_begin + tile) * FT;
+      if (a.hubs_only && tile == 0 && tid == 0) a.hub_slot[row] = hub_index;
       const long long s = a.crow[row];
       const long long e = a.crow[row + 1];
       const long long a0 = s & ~3ll;  // staging starts on a 4-edge boundary (32 B of col, 16 B of val)
@@ -536,7 +543,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
         if (fbase + i < f) {
           float total_i = 0.f;
           for (int w = 0; w < n_warps; ++w) total_i += s_red[w * FT + i];
-          float* dst = a.y + static_cast<size_t>(row) * f + fbase + i;
+          float* dst = a.y + static_cast<size_t>(a.hubs_only ? hub_index : row) * f + fbase + i;
           if (a.accumulate) total_i += *dst;
           st_stream1(dst, total_i);
         }
@@ -544,6 +551,8 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
     }
     if (!alive) return;
   }
+
+  if (a.hubs_only) return;
 
   // ------------------------------------------------------------------ queue 1: light rows
   const int n_short = a.header->n_short;
@@ -714,6 +723,7 @@ static int launch_instance(const SpmmArgs& args, int warps, cudaStream_t stream,
   const int grid = sm_count(device) * per_sm;
   kernel<<<grid, threads, smem, stream>>>(args);
   ASG_CUDA(cudaGetLastError());
+  if (args.hubs_only) return ASG_OK;
   // queue 2 (rows of fewer than 32 edges); leaves at once when the plan has none
   auto short_kernel = args.pack_short ? spmm_short_kernel<VW, G, NV, U, HAS_VAL, true>
                                        : spmm_short_kernel<VW, G, NV, U, HAS_VAL, false>;
@@ -767,7 +777,7 @@ static bool aligned_to(const void* p, size_t n) { return (reinterpret_cast<uintp
 static int spmm_entry(const int64_t* crow, const int64_t* col, const float* val, const float* x, float* y,
                       int64_t n_rows, int64_t nnz, int64_t f, int feature_tile, int warps, int64_t hub_threshold,
                       unsigned flags, void* workspace, size_t workspace_bytes, void* stream_ptr,
-                      int64_t feature_begin = 0, int64_t feature_count = 0) {
+                      int64_t feature_begin = 0, int64_t feature_count = 0, int* hub_slot = nullptr) {
   ASG_REQUIRE(n_rows >= 0 && nnz >= 0 && f >= 0, ASG_EINVAL, "sizes must be non-negative");
   ASG_REQUIRE(n_rows <= 2147483647ll - 2048 && f <= 2147483647ll, ASG_ERANGE,
               "SpMM dimensions exceed the kernel index range");
@@ -824,7 +834,17 @@ static int spmm_entry(const int64_t* crow, const int64_t* col, const float* val,
   args.selftest_stall = (flags & ASG_FLAG_SELFTEST_STALL) ? 1 : 0;
   args.wait_limit_ns = args.selftest_stall ? 20000000ull : kWaitLimitNs;
   args.bulk_stage = (!(flags & ASG_FLAG_NO_BULK_STAGE) && aligned_to(col, 16) && (val == nullptr || aligned_to(val, 16))) ? 1 : 0;
+  args.hubs_only = hub_slot != nullptr ? 1 : 0;
+  args.hub_slot = hub_slot;
   return launch_spmm(args, vw, feature_tile, warps, stream, guard.target);
+}
+
+int spmm_hub_rows_compact(const int64_t* crow, const int64_t* col, const float* val, const float* x, float* hub_y,
+                          int* hub_slot, int64_t n_rows, int64_t nnz, int64_t f, int feature_tile, int warps,
+                          int64_t hub_threshold, unsigned flags, void* workspace, size_t workspace_bytes,
+                          cudaStream_t stream) {
+  return spmm_entry(crow, col, val, x, hub_y, n_rows, nnz, f, feature_tile, warps, hub_threshold, flags, workspace,
+                    workspace_bytes, stream, 0, 0, hub_slot);
 }
 
 }  // namespace asg

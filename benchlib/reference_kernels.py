@@ -26,8 +26,15 @@ OUTPUT = ROOT / "baseline" / "_ref" / "libautosage_cuda.so"
 SOURCES = ("spmm_binding.cpp", "spmm_csr_vec4.cu", "launcher_spmm.cu", "spmm_hub.cu", "spmm_rows.cu", "sddmm_csr_op.cu")
 
 
-def build(reference: Path = Path("/root/reference"), force: bool = False) -> Path | None:
+def reference_checkout() -> Path:
+    """Where the reference's sources are looked for: $AUTOSAGE_REFERENCE_DIR, else a `reference` folder
+    beside this repository."""
+    return Path(os.environ.get("AUTOSAGE_REFERENCE_DIR", str(ROOT.parent / "reference")))
+
+
+def build(reference: Path | None = None, force: bool = False) -> Path | None:
     """Returns the library's path, or None when there is neither a reference checkout nor a prebuilt file."""
+    reference = reference_checkout() if reference is None else reference
     csrc = reference / "csrc"
     if not csrc.is_dir():
         return OUTPUT if OUTPUT.is_file() else None

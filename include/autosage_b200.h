@@ -237,6 +237,30 @@ int asg_linear_bias_umma(const float* x, const float* weight, const float* bias,
                          void* stream);
 
 /*
+ * out[n_rows, out_features] = (A x) @ weight^T + bias, the whole forward of the reference layer
+ * (autosage/conv.py:54-55: spmm_csr, then nn.Linear), with the aggregated rows kept on chip
+ * (csrc/asg_conv_fused.cu).  Rows of hub_threshold edges or more are aggregated by a first launch (the
+ * CTA-per-hub path, hub_warps warps per CTA) into a side buffer in the workspace; a second, persistent
+ * kernel aggregates every other row of a 128-row tile in registers, writes it as bfloat16 pieces into
+ * shared memory, multiplies the tile with the weight on the tensor cores (tcgen05, accumulators in tensor
+ * memory, float32 accuracy as asg_linear_bias_umma) and writes only the output.
+ * Accepted by asg_conv_fused_supported(): in_features 64 or 128, out_features a multiple of 32 up to 256.
+ * x and out 32-byte aligned, dense row-major; val and bias may be null.  flags: ASG_FLAG_PLAN_READY (the
+ * plan workspace already holds the plan of crow for hub_threshold), ASG_FLAG_NO_BULK_STAGE.
+ * plan_workspace: asg_workspace_bytes(n_rows) bytes; workspace:
+ * asg_conv_fused_workspace_bytes(n_rows, nnz, in_features, out_features, hub_threshold) bytes, 256-byte
+ * aligned, whose status word asg_workspace_status() reads (non-zero: a bounded wait gave up, the output
+ * is invalid).  The reference has no counterpart: it runs the two steps as separate PyTorch calls.
+ */
+int asg_conv_fused_supported(int64_t in_features, int64_t out_features);
+size_t asg_conv_fused_workspace_bytes(int64_t n_rows, int64_t nnz, int64_t in_features, int64_t out_features,
+                                      int64_t hub_threshold);
+int asg_conv_fused(const int64_t* crow, const int64_t* col, const float* val, const float* x, const float* weight,
+                   const float* bias, float* out, int64_t n_rows, int64_t nnz, int64_t in_features,
+                   int64_t out_features, int64_t hub_threshold, int hub_warps, unsigned flags, void* plan_workspace,
+                   size_t plan_workspace_bytes, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Pitched device-to-device copy of `height` rows of `width_bytes` bytes (cudaMemcpy2DAsync; runs on
  * the copy engines).  Either pointer may be peer-mapped memory of another GPU.
  */

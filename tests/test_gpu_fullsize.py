@@ -208,6 +208,16 @@ def test_c5_spmm_and_layer_against_oracle(asg, orc, products_like, f):
     error = np.abs(out[subset.rows].double().cpu().numpy() - exact_out)
     assert bool((error <= bound).all()), f"layer F={f}: worst error/bound = {float((error / bound).max()):.3f}"
     del y, out
+    if f == 128:
+        # the one-kernel form of the layer (aggregated rows kept on chip) against the same float64 rows
+        from autosage_b200 import _native
+
+        fused = torch.empty(n, 256, device=x.device)
+        ws = _native.conv_fused(crow, col, None, x, linear.weight.detach(), linear.bias.detach(), fused)
+        assert _native.workspace_status(ws) == 0
+        error = np.abs(fused[subset.rows].double().cpu().numpy() - exact_out)
+        assert bool((error <= bound).all()), f"fused layer: worst error/bound = {float((error / bound).max()):.3f}"
+        del fused, ws
     y = torch.ops.autosage.spmm_csr(crow, col, None, x)
     subset.check_rows(orc, y[subset.rows], exact, f"spmm_csr F={f}")
 
