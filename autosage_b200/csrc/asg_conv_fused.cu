@@ -26,12 +26,12 @@
 // word and a CTA-wide abort flag, the loader waits for its copies in flight, and the CTA leaves through
 // the common exit, which frees its tensor memory.
 //
-// Measured on the 2.45 M-row, 123 M-edge power-law graph (128 -> 256 features): 11.3 ms at
+// Measured on the 2.45 M-row, 123 M-edge power-law graph (128 -> 256 features): 10.95 ms at
 // hub_threshold 64 against 9.8-10.0 ms for the SpMM kernels followed by asg_linear_bias_umma, so the
 // layer keeps the two-kernel path by default.  One CTA per SM (the operand buffers fill shared memory)
 // caps the gather at 18 warps x 6 loads in flight, where the stand-alone SpMM kernels keep 16-32 warps
-// x 8 edges in flight with nothing else resident; the gather here is latency-bound (35 % of DRAM
-// bandwidth, 78 % of stall cycles on the scoreboard of global loads), and what fusion saves - 2.5 GB of
+// x 8 edges in flight with nothing else resident; the gather here is latency-bound (45 % of DRAM
+// bandwidth, 72 % of stall cycles on the scoreboard of global loads), and what fusion saves - 2.5 GB of
 // the 69 GB the layer moves - is less than that loss.
 #include "asg_umma.cuh"
 #include "asg_tile.cuh"
