@@ -105,6 +105,7 @@ def _single_gpu_extras(args, bench, shard, layer, algorithmic, n, nnz, f, out_f,
                                     "ms_per_step": round(ms, 4),
                                     "value": round(algorithmic / (ms * 1e-3) / 1e9, 2), "unit": "GB/s"}
         del matrix
+        extras["fused_layer_kernel"] = _fused_layer_case(shard, layer, x, f, out_f, device)
     if not args.no_cpu_baseline:
         sub = argparse.Namespace(**vars(args))
         sub.steps, sub.warmup = 2, 1
@@ -154,6 +155,37 @@ def _single_gpu_extras(args, bench, shard, layer, algorithmic, n, nnz, f, out_f,
             for label, workload in (("c2_spmm", "c2_spmm"), ("c3_sddmm", "c3_sddmm"), ("c5_spmm", "c5_spmm"))}
         extras["probe_ms_uncached"] = _probe_costs(bench, args, device)
     return extras
+
+
+def _fused_layer_case(shard, layer, x, f, out_f, device) -> dict:
+    """The same layer forward as ONE kernel (aggregation + Linear fused, asg_conv_fused): median of five
+    calls and the largest difference from the default two-kernel forward.  Reported beside the headline
+    because it is the slower form on this graph, which is why the layer does not take it by default."""
+    from autosage_b200 import _native
+
+    if shard.val is not None or not _native.conv_fused_supported(f, out_f):
+        return {"unavailable": "the fused kernel takes 64 or 128 input features and up to 256 output features"}
+    try:
+        weight = layer.linear.weight.detach().contiguous()
+        bias = None if layer.linear.bias is None else layer.linear.bias.detach().contiguous()
+        expected = layer.forward()     # the default forward of the single-GPU layer (x is already loaded)
+        out = torch.empty(x.size(0), out_f, device=device)
+        workspace = _native.conv_fused(shard.crow, shard.col, None, x, weight, bias, out)
+        times = []
+        for _ in range(5):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            _native.conv_fused(shard.crow, shard.col, None, x, weight, bias, out, workspace=workspace)
+            end.record()
+            end.synchronize()
+            times.append(begin.elapsed_time(end))
+        found = {"entry_point": "asg_conv_fused", "hub_threshold": _native.CONV_FUSED_HUB_THRESHOLD,
+                 "ms_per_step": round(sorted(times)[2], 4), "status": _native.workspace_status(workspace),
+                 "gpu_launches_per_step": 3}
+        found["max_abs_difference_from_default"] = float((out - expected).abs().max())
+        return found
+    except Exception as exc:  # noqa: BLE001 - the headline line must still be printed
+        return {"error": f"{type(exc).__name__}: {exc}"}
 
 
 def _probe_costs(bench, args, device) -> dict:
