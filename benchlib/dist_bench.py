@@ -478,7 +478,9 @@ def run(args):
             drained[i % 2].record(drain)
         out.record_stream(drain)
 
-    e2e_steps = max(2, min(args.steps, 5))
+    # enough steps for the streamed form to show its steady state: the first step's copy-in and compute are
+    # not hidden behind a copy-out, and with five steps that start-up is a seventh of the figure
+    e2e_steps = max(2, min(args.steps, 20))
 
     def time_e2e(run_steps):
         run_steps(1)
