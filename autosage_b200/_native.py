@@ -60,6 +60,7 @@ SIGNATURES = {
     "asg_linear_workspace_bytes": (_SZ, [_I64, _I64]),
     "asg_linear_supported": (_INT, [_I64, _I64]),
     "asg_linear_bias_umma": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _P, _SZ, _P]),
+    "asg_linear_bias_umma_ex": (_INT, [_P, _P, _P, _P, _I64, _I64, _I64, _U32, _P, _SZ, _P]),
     "asg_conv_fused_supported": (_INT, [_I64, _I64]),
     "asg_conv_fused_workspace_bytes": (_SZ, [_I64, _I64, _I64, _I64, _I64]),
     "asg_conv_fused": (_INT, [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _INT, _U32, _P, _SZ, _P, _SZ, _P]),
@@ -386,15 +387,15 @@ def linear_umma_supported(in_features: int, out_features: int) -> bool:
 
 
 def linear_bias_umma(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                     workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     workspace: Optional[torch.Tensor] = None, flags: int = 0) -> torch.Tensor:
     """out = x @ weight^T + bias from the hand-written tcgen05 kernel; returns the workspace used (its
     header carries the kernel's status word)."""
     if workspace is None:
         workspace = torch.empty(int(library().asg_linear_workspace_bytes(x.size(1), weight.size(0))), dtype=torch.uint8,
                                 device=x.device)
-    check(library().asg_linear_bias_umma(x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(),
-                                         out.data_ptr(), x.size(0), x.size(1), weight.size(0), workspace.data_ptr(),
-                                         workspace.numel(), _stream(x.device)))
+    check(library().asg_linear_bias_umma_ex(x.data_ptr(), weight.data_ptr(), None if bias is None else bias.data_ptr(),
+                                            out.data_ptr(), x.size(0), x.size(1), weight.size(0), int(flags),
+                                            workspace.data_ptr(), workspace.numel(), _stream(x.device)))
     return workspace
 
 
@@ -408,7 +409,8 @@ CONV_FUSED_HUB_WARPS = 4
 
 def conv_fused(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor], x: torch.Tensor, weight: torch.Tensor,
                bias: Optional[torch.Tensor], out: torch.Tensor, hub_threshold: int = CONV_FUSED_HUB_THRESHOLD,
-               hub_warps: int = CONV_FUSED_HUB_WARPS, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+               hub_warps: int = CONV_FUSED_HUB_WARPS, workspace: Optional[torch.Tensor] = None,
+               extra_flags: int = 0) -> torch.Tensor:
     """out = (A x) @ weight^T + bias in one pass: the aggregated rows stay in shared memory (hub rows, of
     ``hub_threshold`` edges or more, take a first launch into a compact side buffer).  Returns the
     workspace used; its header carries the kernel's status word."""
@@ -419,7 +421,8 @@ def conv_fused(crow: torch.Tensor, col: torch.Tensor, val: Optional[torch.Tensor
     plan, flags = planned_workspace(crow, int(hub_threshold))
     check(library().asg_conv_fused(crow.data_ptr(), col.data_ptr(), None if val is None else val.data_ptr(), x.data_ptr(),
                                    weight.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), n_rows,
-                                   nnz, x.size(1), weight.size(0), int(hub_threshold), int(hub_warps), flags,
+                                   nnz, x.size(1), weight.size(0), int(hub_threshold), int(hub_warps),
+                                   flags | int(extra_flags),
                                    plan.data_ptr(), plan.numel(), workspace.data_ptr(), workspace.numel(),
                                    _stream(x.device)))
     _plan_was_built(plan)

@@ -61,6 +61,7 @@ constexpr int kBStages = 2;
 constexpr int kBStageBytes = (kMaxN / 2) * kSwizzleRowBytes;          // 16 KB: half of the output columns
 constexpr unsigned long long kWaitLimitNs = 500ull * 1000ull * 1000ull;
 constexpr int kStatusWaitExpired = 3;
+constexpr unsigned long long kSelftestLimitNs = 20ull * 1000ull * 1000ull;   // the self-test's wait gives up after 20 ms
 
 struct Smem {
   static constexpr int a_buffers = 0;
@@ -76,6 +77,8 @@ struct Barriers {
   uint64_t a_full[2], a_empty[2];
   uint64_t b_full[kBStages], b_empty[kBStages];
   uint64_t acc_full[2], acc_empty[2];
+  uint64_t mma_done;   // the MMA thread's last commit when it leaves early
+  uint64_t idle;       // self-test: nothing ever arrives here
   uint32_t tmem_base;
   int abort;
   int next_group;
@@ -97,6 +100,7 @@ struct Args {
   int rows, k, n;
   int n_tiles;
   unsigned tmem_columns;
+  int selftest_stall;  // ASG_FLAG_SELFTEST_STALL: the MMA thread waits, before its second tile, on a barrier nothing arrives on
 };
 
 // VW floats of a dense row per lane: a 64-bit or a 128-bit load.
@@ -147,6 +151,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_fused_kernel(const Args a) {
       mbar_init(&bars->b_full[i], 1);
       mbar_init(&bars->b_empty[i], 1);
     }
+    mbar_init(&bars->mma_done, 1);
+    mbar_init(&bars->idle, 1);
     bars->abort = 0;
     bars->next_group = 0;
     mbar_fence_init();
@@ -181,9 +187,15 @@ __global__ void __launch_bounds__(kThreads, 1) conv_fused_kernel(const Args a) {
       bool alive = true;
       for (int j = 0; j < my_tiles && alive; ++j) {
         const unsigned buf = j & 1u;
+        if (a.selftest_stall && j == 1 && !mbar_wait_or_abort(&bars->idle, 0u, abort_flag, kSelftestLimitNs)) {
+          give_up();
+          alive = false;
+          break;
+        }
         if (!mbar_wait_or_abort(&bars->acc_empty[buf], ((j >> 1) & 1u) ^ 1u, abort_flag, kWaitLimitNs) ||
             !mbar_wait_or_abort(&bars->a_full[buf], (j >> 1) & 1u, abort_flag, kWaitLimitNs)) {
           give_up();
+          alive = false;
           break;
         }
         fence_after_thread_sync();
@@ -219,6 +231,12 @@ __global__ void __launch_bounds__(kThreads, 1) conv_fused_kernel(const Args a) {
           mma_commit(&bars->a_empty[buf]);
           mma_commit(&bars->acc_full[buf]);
         }
+      }
+      if (!alive || *abort_flag != 0) {
+        // leaving early: tensor memory is freed at the common exit, so the MMAs issued so far have to be
+        // complete by then (bounded wait on a commit of their own)
+        mma_commit(&bars->mma_done);
+        mbar_wait_bounded(&bars->mma_done, 0u, kWaitLimitNs);
       }
     }
   } else if (warp == 1) {
@@ -575,6 +593,7 @@ extern "C" int asg_conv_fused(const int64_t* crow, const int64_t* col, const flo
   unsigned columns = 32;
   while (columns < 2u * static_cast<unsigned>(n)) columns <<= 1;  // two accumulators, a power of two >= 32
   args.tmem_columns = columns;
+  args.selftest_stall = (flags & ASG_FLAG_SELFTEST_STALL) ? 1 : 0;
   const int sms = sm_count(guard.target);
   const int grid = args.n_tiles < sms ? args.n_tiles : sms;
   auto launch = [&](auto kernel) -> int {

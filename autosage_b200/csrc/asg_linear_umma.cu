@@ -46,6 +46,7 @@ constexpr int kStagingBytes = 8 * 32 * kStagingRow * 4;            // one 32 x 3
 constexpr unsigned long long kWaitLimitNs = 500ull * 1000ull * 1000ull;
 
 constexpr int kStatusWaitExpired = 2;
+constexpr unsigned long long kSelftestLimitNs = 20ull * 1000ull * 1000ull;   // the self-test's wait gives up after 20 ms
 
 struct Smem {
   static constexpr int a_ring = 0;
@@ -61,6 +62,8 @@ struct Barriers {
   uint64_t a_full[kAStages], a_empty[kAStages];
   uint64_t b_full[kBStages], b_empty[kBStages];
   uint64_t acc_full[2], acc_empty[2];
+  uint64_t mma_done;   // the MMA thread's last commit when it leaves early
+  uint64_t idle;       // self-test: nothing ever arrives here
   uint32_t tmem_base;
   int abort;
 };
@@ -76,6 +79,7 @@ struct Args {
   int rows, k, n;
   int k_blocks, n_tiles;
   unsigned tmem_columns;
+  int selftest_stall;  // ASG_FLAG_SELFTEST_STALL: the MMA thread waits, before its second tile, on a barrier nothing arrives on
 };
 
 // One thread per weight element: split it and store the pieces where the MMA will read them.
@@ -122,6 +126,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const Args a) {
       mbar_init(&bars->acc_full[i], 1);
       mbar_init(&bars->acc_empty[i], kEpilogueWarps);
     }
+    mbar_init(&bars->mma_done, 1);
+    mbar_init(&bars->idle, 1);
     bars->abort = 0;
     mbar_fence_init();
   }
@@ -152,8 +158,14 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const Args a) {
       bool alive = true;
       for (int tile = first_tile; tile < a.n_tiles && alive; tile += tile_step, ++it) {
         const unsigned buf = it & 1u;
+        if (a.selftest_stall && it == 1 && !mbar_wait_or_abort(&bars->idle, 0u, abort_flag, kSelftestLimitNs)) {
+          give_up();
+          alive = false;
+          break;
+        }
         if (!mbar_wait_or_abort(&bars->acc_empty[buf], ((it >> 1) & 1u) ^ 1u, abort_flag, kWaitLimitNs)) {
           give_up();
+          alive = false;
           break;
         }
         fence_after_thread_sync();
@@ -192,6 +204,12 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const Args a) {
         }
         if (alive) mma_commit(&bars->acc_full[buf]);
       }
+      if (!alive || *abort_flag != 0) {
+        // leaving early: tensor memory is freed at the common exit, so the MMAs issued so far have to be
+        // complete by then (bounded wait on a commit of their own)
+        mma_commit(&bars->mma_done);
+        mbar_wait_bounded(&bars->mma_done, 0u, kWaitLimitNs);
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------------ weight loader
@@ -210,6 +228,13 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const Args a) {
           mbar_expect_tx(&bars->b_full[sb], stage_bytes);
           bulk_g2s(smem + Smem::b_ring + sb * kBStageStride, a.packed + static_cast<size_t>(s) * stage_bytes, stage_bytes,
                    &bars->b_full[sb]);
+        }
+      }
+      if (!alive || *abort_flag != 0) {
+        // leaving early: wait (bounded) for the copies still in flight into this CTA's shared memory
+        for (unsigned back = 1; back <= kBStages && back <= ib; ++back) {
+          const unsigned use = ib - back;
+          mbar_wait_bounded(&bars->b_full[use % kBStages], (use / kBStages) & 1u, kWaitLimitNs);
         }
       }
     }
@@ -346,9 +371,9 @@ extern "C" int asg_linear_supported(int64_t in_features, int64_t out_features) {
              : 0;
 }
 
-extern "C" int asg_linear_bias_umma(const float* x, const float* weight, const float* bias, float* out, int64_t rows,
-                                    int64_t in_features, int64_t out_features, void* workspace, size_t workspace_bytes,
-                                    void* stream_ptr) {
+extern "C" int asg_linear_bias_umma_ex(const float* x, const float* weight, const float* bias, float* out, int64_t rows,
+                                       int64_t in_features, int64_t out_features, unsigned flags, void* workspace,
+                                       size_t workspace_bytes, void* stream_ptr) {
   using namespace asg;
   using namespace asg::linear_umma;
   ASG_REQUIRE(rows >= 0, ASG_EINVAL, "rows must be non-negative");
@@ -387,10 +412,18 @@ extern "C" int asg_linear_bias_umma(const float* x, const float* weight, const f
   unsigned columns = 32;
   while (columns < 2u * static_cast<unsigned>(n)) columns <<= 1;  // two accumulators, a power of two >= 32
   args.tmem_columns = columns;
+  args.selftest_stall = (flags & ASG_FLAG_SELFTEST_STALL) ? 1 : 0;
   ASG_CUDA(cudaFuncSetAttribute(linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynamicSmem));
   const int sms = sm_count(guard.target);
   const int grid = args.n_tiles < sms ? args.n_tiles : sms;
   linear_kernel<<<grid, kThreads, kDynamicSmem, stream>>>(args);
   ASG_CUDA(cudaGetLastError());
   return ASG_OK;
+}
+
+extern "C" int asg_linear_bias_umma(const float* x, const float* weight, const float* bias, float* out, int64_t rows,
+                                    int64_t in_features, int64_t out_features, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  return asg_linear_bias_umma_ex(x, weight, bias, out, rows, in_features, out_features, 0u, workspace, workspace_bytes,
+                                 stream);
 }

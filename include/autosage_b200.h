@@ -54,9 +54,12 @@ extern "C" {
 #define ASG_FLAG_NO_BULK_STAGE 8u /* hub rows: stage col/val with plain loads, not bulk copies */
 #define ASG_FLAG_NO_TILE_PASSES 16u /* SDDMM: never split the feature dimension into 64-wide passes */
 #define ASG_FLAG_PACK_SHORT_ROWS 32u /* SpMM: rows under 32 edges one per lane group (for very short rows) */
-#define ASG_FLAG_SELFTEST_STALL 64u /* SpMM self-test: the hub staging waits on a barrier nobody arrives on, so
-                                       its bounded wait (20 ms here) gives up, the status word becomes 1 and the
-                                       kernel returns with the hub rows unwritten; nothing faults or hangs */
+#define ASG_FLAG_SELFTEST_STALL 64u /* self-test of the give-up path: one wait inside the kernel is pointed at a
+                                       barrier nothing arrives on, so it runs out (after 20 ms here), the
+                                       status word is set and the kernel returns with part of its output
+                                       unwritten; nothing faults or hangs.  asg_spmm_csr_ex: the hub staging
+                                       wait, status 1.  asg_linear_bias_umma_ex (status 2) and asg_conv_fused
+                                       (status 3): the MMA thread's wait before its second tile */
 
 /* Library version: major*10000 + minor*100 + patch. */
 int asg_version(void);
@@ -235,6 +238,11 @@ int asg_linear_supported(int64_t in_features, int64_t out_features);
 int asg_linear_bias_umma(const float* x, const float* weight, const float* bias, float* out, int64_t rows,
                          int64_t in_features, int64_t out_features, void* workspace, size_t workspace_bytes,
                          void* stream);
+/* As asg_linear_bias_umma, plus ASG_FLAG_SELFTEST_STALL (the MMA thread's wait before its second tile
+ * runs out after 20 ms: status 2, part of the output unwritten, nothing faults or hangs). */
+int asg_linear_bias_umma_ex(const float* x, const float* weight, const float* bias, float* out, int64_t rows,
+                            int64_t in_features, int64_t out_features, unsigned flags, void* workspace,
+                            size_t workspace_bytes, void* stream);
 
 /*
  * out[n_rows, out_features] = (A x) @ weight^T + bias, the whole forward of the reference layer
@@ -246,7 +254,8 @@ int asg_linear_bias_umma(const float* x, const float* weight, const float* bias,
  * memory, float32 accuracy as asg_linear_bias_umma) and writes only the output.
  * Accepted by asg_conv_fused_supported(): in_features 64 or 128, out_features a multiple of 32 up to 256.
  * x and out 32-byte aligned, dense row-major; val and bias may be null.  flags: ASG_FLAG_PLAN_READY (the
- * plan workspace already holds the plan of crow for hub_threshold), ASG_FLAG_NO_BULK_STAGE.
+ * plan workspace already holds the plan of crow for hub_threshold), ASG_FLAG_NO_BULK_STAGE,
+ * ASG_FLAG_SELFTEST_STALL.
  * plan_workspace: asg_workspace_bytes(n_rows) bytes; workspace:
  * asg_conv_fused_workspace_bytes(n_rows, nnz, in_features, out_features, hub_threshold) bytes, 256-byte
  * aligned, whose status word asg_workspace_status() reads (non-zero: a bounded wait gave up, the output

@@ -129,3 +129,27 @@ def test_layer_takes_the_fused_kernel_when_asked(lib, monkeypatch):
     assert info["choice"] == "native"
     out.sum().backward()
     assert x.grad is not None
+
+
+def test_conv_fused_bounded_wait_gives_up_and_reports(lib, orc):
+    """Self-test flag: the MMA thread waits on a barrier nothing arrives on; the wait runs out after
+    20 ms, every warp of the CTA leaves through the common exit and the status word says so.  The next
+    call on the same workspace is complete and correct."""
+    dev = torch.device("cuda")
+    rows = 40_000                                            # more tiles than SMs: every CTA owns a second tile
+    crow, col = random_csr(rows, 10, seed=11, hubs={5: 300, 20_000: 900})
+    x = dense(rows, 128, 12)
+    gen = torch.Generator().manual_seed(13)
+    weight = torch.randn(256, 128, generator=gen) / 128 ** 0.5
+    bias = torch.randn(256, generator=gen)
+    args = (crow.to(dev), col.to(dev), None, x.to(dev), weight.to(dev), bias.to(dev))
+    out = torch.zeros(rows, 256, device=dev)
+    ws = lib.conv_fused(*args, out, extra_flags=lib.FLAG_SELFTEST_STALL)
+    torch.cuda.synchronize()
+    assert lib.workspace_status(ws) == 3
+    ws = lib.conv_fused(*args, out, workspace=ws)
+    torch.cuda.synchronize()
+    assert lib.workspace_status(ws) == 0
+    exact, bound = layer_reference(orc, crow, col, None, x, weight, bias)
+    error = np.abs(out.double().cpu().numpy() - exact)
+    assert bool((error <= bound).all())

@@ -609,6 +609,27 @@ def test_linear_bias_umma_rejects_other_sizes(lib):
         lib.linear_bias_umma(x, weight, None, out)
 
 
+def test_linear_bias_umma_bounded_wait_gives_up_and_reports(lib):
+    """Self-test flag: the MMA thread's wait before its second tile is pointed at a barrier nothing arrives
+    on; it runs out after 20 ms, every warp leaves through the common exit (tensor memory freed, copies in
+    flight waited for) and the status word is 2.  The next call on the same workspace is complete."""
+    dev = torch.device("cuda")
+    rows, k, n = 50_000, 128, 256                         # more tiles than SMs: every CTA owns a second tile
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(rows, k, generator=gen).to(dev)
+    weight = (torch.randn(n, k, generator=gen) / k ** 0.5).to(dev)
+    bias = torch.randn(n, generator=gen).to(dev)
+    out = torch.zeros(rows, n, device=dev)
+    ws = lib.linear_bias_umma(x, weight, bias, out, flags=lib.FLAG_SELFTEST_STALL)
+    torch.cuda.synchronize()
+    assert lib.workspace_status(ws) == 2
+    lib.linear_bias_umma(x, weight, bias, out, ws)
+    torch.cuda.synchronize()
+    assert lib.workspace_status(ws) == 0
+    exact = x.double() @ weight.double().t() + bias.double()
+    assert bool(((out.double() - exact).abs() <= 1e-5 * exact.abs() + 1e-5 * k ** 0.5).all())
+
+
 def test_linear_bias_rejects_unaligned_sizes(lib):
     dev = torch.device("cuda")
     x, weight, out = torch.zeros(8, 6, device=dev), torch.zeros(4, 6, device=dev), torch.zeros(8, 4, device=dev)
