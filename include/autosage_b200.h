@@ -259,7 +259,9 @@ int asg_linear_bias_umma_ex(const float* x, const float* weight, const float* bi
  * plan_workspace: asg_workspace_bytes(n_rows) bytes; workspace:
  * asg_conv_fused_workspace_bytes(n_rows, nnz, in_features, out_features, hub_threshold) bytes, 256-byte
  * aligned, whose status word asg_workspace_status() reads (non-zero: a bounded wait gave up, the output
- * is invalid).  The reference has no counterpart: it runs the two steps as separate PyTorch calls.
+ * is invalid).  The workspace is sized for the worst case, min(n_rows, nnz / hub_threshold) hub rows of
+ * in_features floats (the number of hub rows is known on the device only); only the rows that exist are
+ * touched.  The reference has no counterpart: it runs the two steps as separate PyTorch calls.
  */
 int asg_conv_fused_supported(int64_t in_features, int64_t out_features);
 size_t asg_conv_fused_workspace_bytes(int64_t n_rows, int64_t nnz, int64_t in_features, int64_t out_features,
