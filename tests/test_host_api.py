@@ -385,3 +385,20 @@ def test_row_sample_keeps_whole_rows():
     empty = _auto._row_sample_csr(torch.zeros(11, dtype=torch.long), torch.zeros(0, dtype=torch.long), None,
                                   fraction=0.5, minimum_rows=2, seed=0)
     assert empty[0].tolist() == [0] * 6 and empty[1].numel() == 0 and empty[2] is None
+
+
+def test_fused_layer_route_is_opt_in_and_cuda_only(monkeypatch):
+    """The one-kernel form of the layer is taken only when AUTOSAGE_CONV_FUSED=1 and the input is a CUDA
+    float32 tensor; on the CPU the layer keeps the reference's path whatever the variable says."""
+    import torch
+    from autosage_b200 import conv
+
+    linear = torch.nn.Linear(128, 256)
+    x = torch.zeros(4, 128)
+    assert not conv._fused_forward_ok(linear, x, None)
+    monkeypatch.setenv("AUTOSAGE_CONV_FUSED", "1")
+    assert not conv._fused_forward_ok(linear, x, None)          # CPU tensor
+    layer = conv.AutoSAGEConv(128, 256, mode="native")
+    edge_index = torch.tensor([[0, 1, 2], [1, 2, 3]])
+    out, info = layer(x, edge_index, return_info=True)
+    assert info["choice"] == "baseline" and out.shape == (4, 256)
