@@ -126,7 +126,35 @@ __device__ __forceinline__ void spmm_short_rows(const SpmmArgs& a, int n_hub, in
             for (int i = 0; i < VW; ++i) acc[v][i] = 0.f;
           }
         }
-        for (int j = 0; j < cnt; j += BU) {
+        // whole batches of edges inside a full feature tile need no predicates or zero fill; only the
+        // row's last, partly filled batch goes through the checked form
+        int j_checked = 0;
+        if (fbase + FT <= f) {
+          const int whole = cnt & ~(BU - 1);
+#pragma unroll 1
+          for (int j = 0; j < whole; j += BU) {
+            float xv[U][NV][VW];
+            float wu[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int src = j + u * EPI + sub;
+              const int c = __shfl_sync(kFull, c_l, src);
+              if (HAS_VAL) wu[u] = __shfl_sync(kFull, w_l, src);
+              const float* xrow = a.x + static_cast<long long>(c) * f;
+#pragma unroll
+              for (int v = 0; v < NV; ++v) VecIO<VW>::load(xv[u][v], xrow + foff[v], pol_keep);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+              for (int v = 0; v < NV; ++v)
+#pragma unroll
+                for (int i = 0; i < VW; ++i)
+                  acc[v][i] = HAS_VAL ? fmaf(wu[u], xv[u][v][i], acc[v][i]) : acc[v][i] + xv[u][v][i];
+          }
+          j_checked = whole;
+        }
+        for (int j = j_checked; j < cnt; j += BU) {
           float xv[U][NV][VW];
           float wu[U];
 #pragma unroll
@@ -604,10 +632,13 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
           c_next = static_cast<int>(ld_index(a.col + p + 32 + lane, pol_stream));
           if (HAS_VAL) w_next = ld_weight(a.val + p + 32 + lane, pol_stream);
         }
-        if (cnt == 32 && tile_full) {
-          // Common case: a full batch inside a full feature tile needs no predicates or zero fill.
+        int j_checked = 0;  // where the predicated batches start
+        if (tile_full) {
+          // Common case: a whole batch of edges inside a full feature tile needs no predicates or zero
+          // fill; only the last, partly filled batch of a row's last chunk goes through the checked form.
+          const int whole = cnt & ~(BU - 1);
 #pragma unroll 1
-          for (int j = 0; j < 32; j += BU) {
+          for (int j = 0; j < whole; j += BU) {
             float xv[U][NV][VW];
             float wu[U];
 #pragma unroll
@@ -627,9 +658,9 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
                 for (int i = 0; i < VW; ++i)
                   acc[v][i] = HAS_VAL ? fmaf(wu[u], xv[u][v][i], acc[v][i]) : acc[v][i] + xv[u][v][i];
           }
-          continue;
+          j_checked = whole;
         }
-        for (int j = 0; j < cnt; j += BU) {
+        for (int j = j_checked; j < cnt; j += BU) {
           float xv[U][NV][VW];
           float wu[U];
 #pragma unroll
