@@ -31,7 +31,12 @@ struct SddmmArgs {
 
 constexpr int kTilePasses = -2;  // SddmmArgs::fixed_tile on the host side: "launch once per tile"
 
-template <int VW, int G, int NV, int U>
+// FULL: the feature count is a multiple of the tile (chosen on the host), so no lane is ever outside the
+// row and the gathers need no predicates.  Every batch then runs as a whole 32-edge batch: the last, partly
+// filled batch of a row is moved back to end at the row's last edge - the edges it shares with the batch
+// before it are computed twice and stored once - and in a row shorter than 32 edges the spare lanes gather
+// the row's first column and store nothing.
+template <int VW, int G, int NV, int U, bool FULL>
 __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, long long first, long long stride,
                                                   int lane, uint64_t pol_keep, uint64_t pol_stream) {
   constexpr int EPI = 32 / G;
@@ -61,6 +66,39 @@ __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, l
   const bool one_tile = a.n_tiles == 1 || a.fixed_tile >= 0;
   if (one_tile) load_q(a.fixed_tile >= 0 ? a.fixed_tile : 0);
 
+  if (FULL) {
+    const long long s_row = a.crow[row];
+    const int edge = l * EPI + sub;
+    for (long long p = first; p < e; p += stride) {
+      long long start = p;
+      int skip = 0;  // leading edges of the batch that an earlier batch has already written
+      if (e - p < 32 && e - s_row >= 32) {
+        start = e - 32;
+        skip = static_cast<int>(p - start);
+      }
+      long long at = start + lane;
+      if (at >= e) at = s_row;
+      const int c_l = static_cast<int>(ld_index(a.col + at, pol_stream));
+      float part[G];
+#pragma unroll
+      for (int i = 0; i < G; ++i) part[i] = 0.f;
+      if (one_tile) {
+        batch_dots_impl<VW, G, NV, U, false>(a.k, f, c_l, 32, sub, q, fvalid, foff, pol_keep, part);
+      } else {
+        for (int tile = 0; tile < a.n_tiles; ++tile) {
+          load_q(tile);
+          batch_dots_impl<VW, G, NV, U, false>(a.k, f, c_l, 32, sub, q, fvalid, foff, pol_keep, part);
+        }
+      }
+      float dot = group_reduce_scatter<G>(part, l);
+      const long long pos = start + edge;
+      if (edge >= skip && pos < e) {
+        if (a.fixed_tile > 0) dot += a.out[pos];  // partial sum of the earlier tiles (earlier launches)
+        st_stream1(a.out + pos, dot);
+      }
+    }
+    return;
+  }
   for (long long p = first; p < e; p += stride) {
     const int cnt = e - p < 32 ? static_cast<int>(e - p) : 32;
     int c_l = 0;
@@ -85,8 +123,10 @@ __device__ __forceinline__ void sddmm_row_batches(const SddmmArgs& a, int row, l
   }
 }
 
-template <int VW, int G, int NV, int U>
-__global__ void __launch_bounds__(512) sddmm_kernel(const SddmmArgs a) {
+// 64-feature tiles (the L2-resident passes): at most 64 registers, so that four 8-warp CTAs fit an SM; the
+// gather is latency-bound there and pays for warps, not for registers.
+template <int VW, int G, int NV, int U, bool FULL>
+__global__ void __launch_bounds__(512, (VW * G * NV <= 64 ? 2 : 1)) sddmm_kernel(const SddmmArgs a) {
   pdl_release_dependents();  // the short-row kernel may move in as CTAs of this one retire
   __shared__ int s_item;
   const int tid = threadIdx.x;
@@ -110,7 +150,7 @@ __global__ void __launch_bounds__(512) sddmm_kernel(const SddmmArgs a) {
       if (item < 0) break;
       const int row = a.order[item];
       const long long s = a.crow[row];
-      sddmm_row_batches<VW, G, NV, U>(a, row, s + 32ll * warp, 32ll * n_warps, lane, pol_keep, pol_stream);
+      sddmm_row_batches<VW, G, NV, U, FULL>(a, row, s + 32ll * warp, 32ll * n_warps, lane, pol_keep, pol_stream);
     }
   }
   const int n_short = a.header->n_short;
@@ -121,7 +161,7 @@ __global__ void __launch_bounds__(512) sddmm_kernel(const SddmmArgs a) {
       const unsigned long long it = warp_next(&a.header->counter[1]);
       if (it >= static_cast<unsigned long long>(n_medium)) break;
       const int row = light[it];
-      sddmm_row_batches<VW, G, NV, U>(a, row, a.crow[row], 32ll, lane, pol_keep, pol_stream);
+      sddmm_row_batches<VW, G, NV, U, FULL>(a, row, a.crow[row], 32ll, lane, pol_keep, pol_stream);
     }
   }
 }
@@ -205,7 +245,8 @@ __global__ void __launch_bounds__(512) sddmm_short_kernel(const SddmmArgs a) {
 
 template <int VW, int G, int NV, int U>
 static int launch_instance(const SddmmArgs& args, int warps, cudaStream_t stream, int device) {
-  auto kernel = sddmm_kernel<VW, G, NV, U>;
+  // whole feature tiles only: the kernel without predicates on the gathers
+  auto kernel = args.f % (VW * G * NV) == 0 ? sddmm_kernel<VW, G, NV, U, true> : sddmm_kernel<VW, G, NV, U, false>;
   const int threads = warps * 32;
   int per_sm = 0;
   ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0));
