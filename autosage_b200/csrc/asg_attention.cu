@@ -213,8 +213,8 @@ __device__ __forceinline__ void attention_load_q(const AttentionArgs& a, int row
 template <int VW, int G, int NV, int U_REQUESTED>
 __device__ __forceinline__ void attention_one_batch(const AttentionArgs& a, int c_l, int cnt, int lane,
                                                     const float (&q)[NV][VW], const bool (&fvalid)[NV],
-                                                    const int (&foff)[NV], uint64_t pol_keep, float& m_run,
-                                                    float& l_run, float (&acc)[NV][VW]) {
+                                                    const int (&foff)[NV], bool tile_full, uint64_t pol_keep,
+                                                    float& m_run, float& l_run, float (&acc)[NV][VW]) {
   constexpr int EPI = 32 / G;
   constexpr int U = U_REQUESTED < G ? U_REQUESTED : G;  // an unrolled batch never exceeds 32 edges
   constexpr int BU = EPI * U;
@@ -243,7 +243,33 @@ __device__ __forceinline__ void attention_one_batch(const AttentionArgs& a, int 
     for (int i = 0; i < VW; ++i) acc[v][i] *= rescale;
 
   // 3. acc += sum_j prob_j * V[col_j]; the probability of edge j sits in lane (j/EPI) + G*(j%EPI)
-  for (int j = 0; j < cnt; j += BU) {
+  int j_checked = 0;
+  if (tile_full) {
+    // whole batches of edges inside a full feature tile: no predicates, no zero fill
+    const int whole = cnt & ~(BU - 1);
+#pragma unroll 1
+    for (int j = 0; j < whole; j += BU) {
+      float xv[U][NV][VW];
+      float wu[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int src = j + u * EPI + sub;
+        const int c = __shfl_sync(kFull, c_l, src);
+        wu[u] = __shfl_sync(kFull, prob, (src / EPI) + G * (src % EPI));
+        const float* vrow = a.v + static_cast<size_t>(c) * f;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) VecIO<VW>::load(xv[u][v], vrow + foff[v], pol_keep);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int v = 0; v < NV; ++v)
+#pragma unroll
+          for (int i = 0; i < VW; ++i) acc[v][i] = fmaf(wu[u], xv[u][v][i], acc[v][i]);
+    }
+    j_checked = whole;
+  }
+  for (int j = j_checked; j < cnt; j += BU) {
     float xv[U][NV][VW];
     float wu[U];
 #pragma unroll
@@ -282,13 +308,17 @@ __device__ __forceinline__ void attention_batches(const AttentionArgs& a, int ro
   bool fvalid[NV];
   int foff[NV];
   attention_load_q<VW, G, NV>(a, row, lane, pol_stream, q, fvalid, foff);
+  bool lane_full = true;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) lane_full = lane_full && fvalid[v];
+  const bool tile_full = __all_sync(kFull, lane_full);  // every lane inside the row: the V gathers need no predicates
   int c_next = 0;  // the next batch's columns are fetched while the current batch gathers
   if (first + lane < e) c_next = static_cast<int>(ld_index(a.col + first + lane, pol_stream));
   for (long long p = first; p < e; p += stride) {
     const int cnt = e - p < 32 ? static_cast<int>(e - p) : 32;
     const int c_l = c_next;
     if (p + stride + lane < e) c_next = static_cast<int>(ld_index(a.col + p + stride + lane, pol_stream));
-    attention_one_batch<VW, G, NV, U>(a, c_l, cnt, lane, q, fvalid, foff, pol_keep, m_run, l_run, acc);
+    attention_one_batch<VW, G, NV, U>(a, c_l, cnt, lane, q, fvalid, foff, tile_full, pol_keep, m_run, l_run, acc);
   }
 }
 
