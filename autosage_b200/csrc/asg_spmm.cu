@@ -54,7 +54,7 @@ constexpr int kChunkPerWarp = 128;  // staged edges per warp and stage in the hu
 // the long-row loops (inlined into the main kernel it cost the long-row workloads about 10 %), launched
 // right after the main kernel as a programmatic dependent: it starts filling SMs as the main kernel's
 // CTAs retire instead of waiting for its last hub row.
-template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL>
+template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL, bool EXTRAS>
 __device__ __forceinline__ void spmm_short_rows(const SpmmArgs& a, int n_hub, int n_medium, int n_short) {
   constexpr int U = U_REQUESTED < G ? U_REQUESTED : G;
   constexpr int EPI = 32 / G;
@@ -113,13 +113,13 @@ __device__ __forceinline__ void spmm_short_rows(const SpmmArgs& a, int n_hub, in
             if (HAS_VAL) w_next = ld_weight(a.val + s_cur + lane, pol_stream);
           }
         }
-        if (cnt == 0 && a.accumulate) continue;  // y += 0
+        if (cnt == 0 && (EXTRAS && a.accumulate)) continue;  // y += 0
         // Accumulating (column blocks of the sharded path): the lanes that will store start from the
         // row's current output, fetched before the gathers so that its latency hides behind them.
         float acc[NV][VW];
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-          if (a.accumulate && sub == 0 && fvalid[v]) {
+          if ((EXTRAS && a.accumulate) && sub == 0 && fvalid[v]) {
             VecIO<VW>::load_plain(acc[v], a.y + static_cast<size_t>(row) * f + foff[v]);
           } else {
 #pragma unroll
@@ -210,7 +210,7 @@ __device__ __forceinline__ void spmm_short_rows(const SpmmArgs& a, int n_hub, in
 // degrees inside a 32-row grab differing by up to 2x) the shared form is faster: paired rows wait for
 // the longer of the two (measured: +10 % on the short-row kernel of the 2.4 M-row graph), so it stays the
 // default.
-template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL>
+template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL, bool EXTRAS>
 __device__ __forceinline__ void spmm_short_rows_packed(const SpmmArgs& a, int n_hub, int n_medium, int n_short) {
   constexpr int U = U_REQUESTED < 4 ? U_REQUESTED : 4;  // X rows in flight per lane group
   constexpr int FT = VW * G * NV;
@@ -288,11 +288,11 @@ __device__ __forceinline__ void spmm_short_rows_packed(const SpmmArgs& a, int n_
         }
         // Accumulating (column blocks of the sharded path): start from the row's current output,
         // fetched before the gathers so that its latency hides behind them.
-        const bool writes = mine < n_here && (cnt > 0 || !a.accumulate);
+        const bool writes = mine < n_here && (cnt > 0 || !(EXTRAS && a.accumulate));
         float acc[NV][VW];
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-          if (a.accumulate && writes && fvalid[v]) {
+          if ((EXTRAS && a.accumulate) && writes && fvalid[v]) {
             VecIO<VW>::load_plain(acc[v], a.y + static_cast<size_t>(row) * f + foff[v]);
           } else {
 #pragma unroll
@@ -349,7 +349,10 @@ __device__ __forceinline__ void spmm_short_rows_packed(const SpmmArgs& a, int n_
   }
 }
 
-template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL>
+// EXTRAS = false is the plain product y = A x: the instances without the accumulate, hub-only and self-test
+// code, whose registers cost the L2-bound workloads a CTA per SM.  The host picks EXTRAS = true when any of
+// those is asked for.
+template <int VW, int G, int NV, int U_REQUESTED, bool HAS_VAL, bool EXTRAS>
 __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
   constexpr int U = U_REQUESTED < G ? U_REQUESTED : G;  // an unrolled batch never exceeds 32 edges
   constexpr int EPI = 32 / G;          // edges per load instruction
@@ -404,7 +407,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
       const int hub_index = item - tile * n_hub;
       const int row = a.order[hub_index];
       const int fbase = (a.tile_begin + tile) * FT;
-      if (a.hubs_only && tile == 0 && tid == 0) a.hub_slot[row] = hub_index;
+      if ((EXTRAS && a.hubs_only) && tile == 0 && tid == 0) a.hub_slot[row] = hub_index;
       const long long s = a.crow[row];
       const long long e = a.crow[row + 1];
       const long long a0 = s & ~3ll;  // staging starts on a 4-edge boundary (32 B of col, 16 B of val)
@@ -469,8 +472,8 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
         if (a.bulk_stage) {
           // self-test: wait on a barrier nobody arrives on (no copy targets it, so nothing is pending
           // on it when the CTA leaves); the staging itself runs and completes as usual
-          uint64_t* awaited = a.selftest_stall ? idle_bar : &bars[st];
-          arrived = mbar_wait_bounded(awaited, a.selftest_stall ? 0u : ((seq >> 1) & 1), a.wait_limit_ns);
+          uint64_t* awaited = (EXTRAS && a.selftest_stall) ? idle_bar : &bars[st];
+          arrived = mbar_wait_bounded(awaited, (EXTRAS && a.selftest_stall) ? 0u : ((seq >> 1) & 1), a.wait_limit_ns);
           if (!arrived) atomicCAS(&a.header->status, 0, kStatusBulkWaitExpired);
         }
         if (arrived) {
@@ -571,8 +574,8 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
         if (fbase + i < f) {
           float total_i = 0.f;
           for (int w = 0; w < n_warps; ++w) total_i += s_red[w * FT + i];
-          float* dst = a.y + static_cast<size_t>(a.hubs_only ? hub_index : row) * f + fbase + i;
-          if (a.accumulate) total_i += *dst;
+          float* dst = a.y + static_cast<size_t>((EXTRAS && a.hubs_only) ? hub_index : row) * f + fbase + i;
+          if ((EXTRAS && a.accumulate)) total_i += *dst;
           st_stream1(dst, total_i);
         }
       }
@@ -580,7 +583,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
     if (!alive) return;
   }
 
-  if (a.hubs_only) return;
+  if ((EXTRAS && a.hubs_only)) return;
 
   // ------------------------------------------------------------------ queue 1: light rows
   const int n_short = a.header->n_short;
@@ -608,7 +611,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
       float acc[NV][VW];
 #pragma unroll
       for (int v = 0; v < NV; ++v) {
-        if (a.accumulate && sub == 0 && fvalid[v]) {
+        if ((EXTRAS && a.accumulate) && sub == 0 && fvalid[v]) {
           VecIO<VW>::load_plain(acc[v], a.y + static_cast<size_t>(row) * f + foff[v]);
         } else {
 #pragma unroll
@@ -711,24 +714,24 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
 // given: with launch bounds (512) alone it keeps registers low for occupancy (best when the gather
 // is served by L2); with (512, 1) it may use 128 registers and schedules loads further ahead, which
 // measured 10 % faster when the gathered rows come from HBM (whole-row 128-float tiles).
-template <int VW, int G, int NV, int U, bool HAS_VAL>
+template <int VW, int G, int NV, int U, bool HAS_VAL, bool EXTRAS>
 __global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
   pdl_release_dependents();  // the short-row kernel may move in as CTAs of this one retire
-  spmm_body<VW, G, NV, U, HAS_VAL>(a);
+  spmm_body<VW, G, NV, U, HAS_VAL, EXTRAS>(a);
 }
-template <int VW, int G, int NV, int U, bool HAS_VAL>
+template <int VW, int G, int NV, int U, bool HAS_VAL, bool EXTRAS>
 __global__ void __launch_bounds__(512, 1) spmm_kernel_deep(const SpmmArgs a) {
   pdl_release_dependents();
-  spmm_body<VW, G, NV, U, HAS_VAL>(a);
+  spmm_body<VW, G, NV, U, HAS_VAL, EXTRAS>(a);
 }
 
-template <int VW, int G, int NV, int U, bool HAS_VAL, bool PACKED>
+template <int VW, int G, int NV, int U, bool HAS_VAL, bool PACKED, bool EXTRAS>
 __global__ void __launch_bounds__(512) spmm_short_kernel(const SpmmArgs a) {
   const int n_hub = a.header->n_hub;
   const int n_short = a.header->n_short;
   if (n_short > 0) {
-    if (PACKED) spmm_short_rows_packed<VW, G, NV, U, HAS_VAL>(a, n_hub, a.header->n_light - n_short, n_short);
-    else spmm_short_rows<VW, G, NV, U, HAS_VAL>(a, n_hub, a.header->n_light - n_short, n_short);
+    if (PACKED) spmm_short_rows_packed<VW, G, NV, U, HAS_VAL, EXTRAS>(a, n_hub, a.header->n_light - n_short, n_short);
+    else spmm_short_rows<VW, G, NV, U, HAS_VAL, EXTRAS>(a, n_hub, a.header->n_light - n_short, n_short);
   }
   pdl_wait_for_primary();  // do not complete before the main kernel has
 }
@@ -741,7 +744,9 @@ static int launch_instance(const SpmmArgs& args, int warps, cudaStream_t stream,
   constexpr int FT = VW * G * NV;
   // whole-row tiles of 128 floats with 256-bit loads are the HBM-streaming configuration
   constexpr bool kDeep = (VW == 8 && FT == 128);
-  auto kernel = kDeep ? spmm_kernel_deep<VW, G, NV, U, HAS_VAL> : spmm_kernel<VW, G, NV, U, HAS_VAL>;
+  const bool extras = args.accumulate || args.hubs_only || args.selftest_stall || args.pack_short;
+  auto kernel = kDeep ? (extras ? spmm_kernel_deep<VW, G, NV, U, HAS_VAL, true> : spmm_kernel_deep<VW, G, NV, U, HAS_VAL, false>)
+                      : (extras ? spmm_kernel<VW, G, NV, U, HAS_VAL, true> : spmm_kernel<VW, G, NV, U, HAS_VAL, false>);
   const int threads = warps * 32;
   const int chunk = kChunkPerWarp * warps;
   const size_t smem = 128 + size_t(24) * chunk + size_t(4) * warps * FT;
@@ -756,8 +761,9 @@ static int launch_instance(const SpmmArgs& args, int warps, cudaStream_t stream,
   ASG_CUDA(cudaGetLastError());
   if (args.hubs_only) return ASG_OK;
   // queue 2 (rows of fewer than 32 edges); leaves at once when the plan has none
-  auto short_kernel = args.pack_short ? spmm_short_kernel<VW, G, NV, U, HAS_VAL, true>
-                                       : spmm_short_kernel<VW, G, NV, U, HAS_VAL, false>;
+  auto short_kernel = args.pack_short ? spmm_short_kernel<VW, G, NV, U, HAS_VAL, true, true>
+                      : extras        ? spmm_short_kernel<VW, G, NV, U, HAS_VAL, false, true>
+                                      : spmm_short_kernel<VW, G, NV, U, HAS_VAL, false, false>;
   int short_per_sm = 0;
   ASG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&short_per_sm, short_kernel, threads, 0));
   if (short_per_sm < 1) short_per_sm = 1;
