@@ -636,10 +636,13 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
           if (HAS_VAL) w_next = ld_weight(a.val + p + 32 + lane, pol_stream);
         }
         int j_checked = 0;  // where the predicated batches start
-        if (tile_full) {
-          // Common case: a whole batch of edges inside a full feature tile needs no predicates or zero
-          // fill; only the last, partly filled batch of a row's last chunk goes through the checked form.
-          const int whole = cnt & ~(BU - 1);
+        // Whole-row tiles (the HBM-streaming configuration): every whole batch of edges takes the form
+        // without predicates and zero fill, only the last, partly filled batch of a row's last chunk the
+        // checked one.  Narrower tiles (gathers served by L2, where warps per SM count most): only whole
+        // 32-edge chunks do, which keeps the kernel at 64 registers.
+        constexpr bool kWholeBatches = (VW == 8 && FT == 128);
+        if (tile_full && (kWholeBatches || cnt == 32)) {
+          const int whole = kWholeBatches ? (cnt & ~(BU - 1)) : 32;
 #pragma unroll 1
           for (int j = 0; j < whole; j += BU) {
             float xv[U][NV][VW];
@@ -661,6 +664,7 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
                 for (int i = 0; i < VW; ++i)
                   acc[v][i] = HAS_VAL ? fmaf(wu[u], xv[u][v][i], acc[v][i]) : acc[v][i] + xv[u][v][i];
           }
+          if (!kWholeBatches || whole == cnt) continue;  // nothing left for the checked form
           j_checked = whole;
         }
         for (int j = j_checked; j < cnt; j += BU) {
@@ -711,11 +715,12 @@ __device__ __forceinline__ void spmm_body(const SpmmArgs& a) {
 }
 
 // Two entry kernels over the same body.  They differ only in the register budget the compiler is
-// given: with launch bounds (512) alone it keeps registers low for occupancy (best when the gather
-// is served by L2); with (512, 1) it may use 128 registers and schedules loads further ahead, which
-// measured 10 % faster when the gathered rows come from HBM (whole-row 128-float tiles).
+// given: with launch bounds (512, 2) it stays at 64 registers, eight 4-warp CTAs per SM (best when the
+// gather is served by L2: left to itself the compiler took 79 and the 233 k-row graph ran 4 % slower);
+// with (512, 1) it may use 128 registers and schedules loads further ahead, which measured 10 % faster
+// when the gathered rows come from HBM (whole-row 128-float tiles).
 template <int VW, int G, int NV, int U, bool HAS_VAL, bool EXTRAS>
-__global__ void __launch_bounds__(512) spmm_kernel(const SpmmArgs a) {
+__global__ void __launch_bounds__(512, 2) spmm_kernel(const SpmmArgs a) {
   pdl_release_dependents();  // the short-row kernel may move in as CTAs of this one retire
   spmm_body<VW, G, NV, U, HAS_VAL, EXTRAS>(a);
 }
