@@ -67,3 +67,23 @@ int asg_workspace_status(const void* workspace, int32_t* host_status, void* stre
 }
 
 }  // extern "C"
+
+namespace asg {
+long long l2_bytes(int device) {
+  static std::mutex lock;
+  static long long cached[64];
+  static bool known[64] = {false};
+  if (device < 0 || device >= 64) device = 0;
+  std::lock_guard<std::mutex> hold(lock);
+  if (!known[device]) {
+    int value = 0;
+    if (cudaDeviceGetAttribute(&value, cudaDevAttrL2CacheSize, device) != cudaSuccess || value <= 0) {
+      cudaGetLastError();
+      value = 126 << 20;
+    }
+    cached[device] = value;
+    known[device] = true;
+  }
+  return cached[device];
+}
+}  // namespace asg

@@ -63,6 +63,7 @@ struct DeviceGuard {
 };
 
 int sm_count(int device);  // cached per device (asg_api.cu)
+long long l2_bytes(int device);  // L2 cache size, cached per device (asg_api.cu)
 
 // ---------------------------------------------------------------------------------------------
 // Workspace layout (device memory owned by the caller).

@@ -42,6 +42,7 @@ struct SpmmArgs {
   // where to find it.  Queues 1 and 2 are not touched.
   int hubs_only;
   int* hub_slot;
+  int streaming;  // host side: X is much larger than L2, the gathers stream from HBM
 };
 
 constexpr int kChunkPerWarp = 128;  // staged edges per warp and stage in the hub path
@@ -747,11 +748,14 @@ __global__ void __launch_bounds__(512) spmm_short_kernel(const SpmmArgs a) {
 template <int VW, int G, int NV, int U, bool HAS_VAL>
 static int launch_instance(const SpmmArgs& args, int warps, cudaStream_t stream, int device) {
   constexpr int FT = VW * G * NV;
-  // whole-row tiles of 128 floats with 256-bit loads are the HBM-streaming configuration
-  constexpr bool kDeep = (VW == 8 && FT == 128);
+  // The entry with the roomy register budget when the gathers stream from HBM: always for whole-row tiles
+  // of 128 floats with 256-bit loads, and for narrower tiles when X is much larger than L2 (there the
+  // 64-register entry lost 8 % on the 2.4 M-row graph; on the 233 k-row graph, whose X fits L2, it wins 4 %).
+  constexpr bool kWholeRow = (VW == 8 && FT == 128);
+  const bool deep = kWholeRow || args.streaming;
   const bool extras = args.accumulate || args.hubs_only || args.selftest_stall || args.pack_short;
-  auto kernel = kDeep ? (extras ? spmm_kernel_deep<VW, G, NV, U, HAS_VAL, true> : spmm_kernel_deep<VW, G, NV, U, HAS_VAL, false>)
-                      : (extras ? spmm_kernel<VW, G, NV, U, HAS_VAL, true> : spmm_kernel<VW, G, NV, U, HAS_VAL, false>);
+  auto kernel = deep ? (extras ? spmm_kernel_deep<VW, G, NV, U, HAS_VAL, true> : spmm_kernel_deep<VW, G, NV, U, HAS_VAL, false>)
+                     : (extras ? spmm_kernel<VW, G, NV, U, HAS_VAL, true> : spmm_kernel<VW, G, NV, U, HAS_VAL, false>);
   const int threads = warps * 32;
   const int chunk = kChunkPerWarp * warps;
   const size_t smem = 128 + size_t(24) * chunk + size_t(4) * warps * FT;
@@ -878,6 +882,10 @@ static int spmm_entry(const int64_t* crow, const int64_t* col, const float* val,
   args.bulk_stage = (!(flags & ASG_FLAG_NO_BULK_STAGE) && aligned_to(col, 16) && (val == nullptr || aligned_to(val, 16))) ? 1 : 0;
   args.hubs_only = hub_slot != nullptr ? 1 : 0;
   args.hub_slot = hub_slot;
+  // Items run tile-major, so what has to stay in L2 during a pass is one feature tile of every X row
+  // (square graphs: X has about n_rows rows).
+  const long long slice = static_cast<long long>(n_rows) * (f < feature_tile ? f : feature_tile) * 4;
+  args.streaming = slice > l2_bytes(guard.target) * 3 / 2 ? 1 : 0;
   return launch_spmm(args, vw, feature_tile, warps, stream, guard.target);
 }
 
